@@ -1,0 +1,230 @@
+// C ABI of libfa_b200.so (declared in include/fa_b200.h): argument validation, TMA descriptor
+// construction and kernel launches.  Mirrors the checks of the reference host API
+// (csrc/flash_attn/fmha_api.cpp:173-299, :302-449) but reports errors through return codes
+// instead of exceptions or exit().
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include "../../include/fa_b200.h"
+#include "fa_kernels.h"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const std::string& msg) {
+  g_last_error = msg;
+  return code;
+}
+
+#define FA_REQUIRE(cond, msg)                                   \
+  do {                                                          \
+    if (!(cond)) return fail(FA_ERR_INVALID_ARGUMENT, (msg));   \
+  } while (0)
+
+#define FA_CUDA(expr)                                                                      \
+  do {                                                                                     \
+    cudaError_t e_ = (expr);                                                               \
+    if (e_ != cudaSuccess)                                                                 \
+      return fail(FA_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e_));        \
+  } while (0)
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up at run time so that the library has no link-time
+// dependency on libcuda and can be loaded (for symbol checks) on a machine without a driver.
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// 3-D map over a [rows, heads, head_dim] tensor with arbitrary row / head strides:
+// dim0 = head_dim, dim1 = rows, dim2 = heads; box = 64 columns x box_rows rows x 1 head, stored
+// with the 128-byte swizzle.  Columns beyond head_dim and rows beyond `rows` read as zero.
+int make_tile_map(CUtensorMap* tm, const void* base, bool bf16, int64_t rows, int heads, int head_dim,
+                  int64_t row_stride, int64_t head_stride, int box_rows) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  FA_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "tensor base must be 16-byte aligned");
+  FA_REQUIRE((row_stride * 2) % 16 == 0 && (head_stride * 2) % 16 == 0,
+             "row and head strides must be multiples of 8 elements");
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(rows),
+                        static_cast<cuuint64_t>(heads)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_stride) * 2,
+                           static_cast<cuuint64_t>(head_stride) * 2};
+  cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  return FA_OK;
+}
+
+int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+int validate_common(const fa_fwd_params* p) {
+  FA_REQUIRE(p != nullptr, "params is null");
+  FA_REQUIRE(p->q && p->k && p->v, "q, k, v must be non-null");
+  FA_REQUIRE(p->cu_seqlens_q && p->cu_seqlens_k, "cu_seqlens must be non-null");
+  FA_REQUIRE(p->batch > 0, "batch must be positive");
+  FA_REQUIRE(p->heads > 0, "heads must be positive");
+  FA_REQUIRE(p->head_dim == 16 || p->head_dim == 32 || p->head_dim == 64 || p->head_dim == 128,
+             "head_dim must be 16, 32, 64 or 128");
+  FA_REQUIRE(p->total_q >= 0 && p->total_k >= 0, "negative token count");
+  FA_REQUIRE(p->max_seqlen_q > 0 && p->max_seqlen_k > 0, "max_seqlen must be positive");
+  FA_REQUIRE(p->p_dropout >= 0.f && p->p_dropout < 1.f, "p_dropout must be in [0, 1)");
+  FA_REQUIRE(p->lse_stride >= p->max_seqlen_q, "softmax_lse rows are shorter than max_seqlen_q");
+  if (p->blockmask) {
+    FA_REQUIRE(!p->is_causal, "block-sparse attention does not support the causal flag");
+    FA_REQUIRE(!p->is_bf16, "block-sparse attention is fp16 only");
+    FA_REQUIRE(p->head_dim <= 64, "block-sparse attention supports head_dim 16, 32, 64");
+  }
+  return FA_OK;
+}
+
+void fill_dropout(const fa_fwd_params* p, fa::KernelArgs* a) {
+  const float p_keep = 1.f - p->p_dropout;
+  a->rp_keep = 1.f / p_keep;
+  a->drop.key0 = static_cast<uint32_t>(p->philox_seed);
+  a->drop.key1 = static_cast<uint32_t>(p->philox_seed >> 32);
+  a->drop.counter_base = p->philox_offset / 4;
+  a->drop.threshold = static_cast<uint32_t>(
+      static_cast<uint16_t>(std::floor(static_cast<double>(p_keep) * 65535.0)));
+  a->drop.n_shift = fa_mask_block_n(p->head_dim, p->max_seqlen_k, p->blockmask != nullptr) == 128 ? 7 : 8;
+  a->drop.heads_total = p->mask_heads_total > 0 ? p->mask_heads_total : p->heads;
+  a->drop.head_offset = p->mask_heads_total > 0 ? p->mask_head_offset : 0;
+}
+
+void fill_args(const fa_fwd_params* p, fa::KernelArgs* a) {
+  std::memset(a, 0, sizeof(*a));
+  a->cu_seqlens_q = p->cu_seqlens_q;
+  a->cu_seqlens_k = p->cu_seqlens_k;
+  a->o = p->o;
+  a->lse = p->softmax_lse;
+  a->o_row_stride = p->o_row_stride;
+  a->o_head_stride = p->o_head_stride;
+  a->lse_stride = p->lse_stride;
+  a->batch = p->batch;
+  a->heads = p->heads;
+  a->head_dim = p->head_dim;
+  a->scale = p->softmax_scale;
+  a->scale_log2 = p->softmax_scale * 1.4426950408889634f;
+  a->status = p->status;
+  fill_dropout(p, a);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* fa_status_string(int status) {
+  switch (status) {
+    case FA_OK: return "ok";
+    case FA_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case FA_ERR_CUDA: return "CUDA error";
+    case FA_ERR_UNSUPPORTED: return "unsupported configuration";
+    case FA_ERR_WORKSPACE: return "workspace missing or too small";
+    default: return "unknown status";
+  }
+}
+
+const char* fa_last_error(void) { return g_last_error.c_str(); }
+
+int fa_device_supported(void) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return fail(FA_ERR_CUDA, "no CUDA device");
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+    return fail(FA_ERR_CUDA, "cannot query the device");
+  if (major != 10) return fail(FA_ERR_UNSUPPORTED, "this library only runs on sm_100 devices");
+  return FA_OK;
+}
+
+int32_t fa_mask_block_n(int32_t head_dim, int32_t max_seqlen_k, int32_t is_blocksparse) {
+  if (is_blocksparse) return 256;
+  if (max_seqlen_k <= 128) return 128;
+  return head_dim == 128 ? 128 : 256;
+}
+
+uint64_t fa_philox_increment(int32_t head_dim, int32_t max_seqlen_q, int32_t max_seqlen_k,
+                             int32_t is_blocksparse) {
+  const int n = fa_mask_block_n(head_dim, max_seqlen_k, is_blocksparse);
+  const int base = is_blocksparse ? 256 : (head_dim == 128 ? 128 : 256);
+  int sk = round_up(max_seqlen_k, base);
+  if (!is_blocksparse) {
+    if (max_seqlen_k <= 128) sk = 128;
+    else if (max_seqlen_k <= 256) sk = 256;
+  }
+  const int sq = round_up(max_seqlen_q, 16);
+  const uint64_t steps = static_cast<uint64_t>(sq / 16);
+  const uint64_t mmas_n = static_cast<uint64_t>(n / 64);
+  const uint64_t loop_steps = static_cast<uint64_t>((sk + n - 1) / n);
+  return steps * mmas_n * 8 * loop_steps;
+}
+
+int fa_fwd(const fa_fwd_params* p, void* cuda_stream) {
+  if (int rc = validate_common(p)) return rc;
+  FA_REQUIRE(p->o && p->softmax_lse, "o and softmax_lse must be non-null");
+  FA_REQUIRE((reinterpret_cast<uintptr_t>(p->o) & 15) == 0, "o must be 16-byte aligned");
+  FA_REQUIRE(p->o_row_stride % 8 == 0 && p->o_head_stride % 8 == 0,
+             "o strides must be multiples of 8 elements");
+  if (p->blockmask) return fail(FA_ERR_UNSUPPORTED, "block-sparse forward is not built yet");
+  if (p->s_dmask) return fail(FA_ERR_UNSUPPORTED, "return_softmax is not built yet");
+
+  fa::FwdLaunch l;
+  std::memset(&l, 0, sizeof(l));
+  fill_args(p, &l.args);
+  l.dpad = p->head_dim <= 64 ? 64 : 128;
+  l.is_bf16 = p->is_bf16 != 0;
+  l.is_causal = p->is_causal != 0;
+  l.is_dropout = p->p_dropout > 0.f;
+  l.max_seqlen_q = p->max_seqlen_q;
+  l.max_seqlen_k = p->max_seqlen_k;
+  if (int rc = make_tile_map(&l.tm_q, p->q, l.is_bf16, p->total_q, p->heads, p->head_dim,
+                             p->q_row_stride, p->q_head_stride, 128)) return rc;
+  if (int rc = make_tile_map(&l.tm_k, p->k, l.is_bf16, p->total_k, p->heads, p->head_dim,
+                             p->k_row_stride, p->k_head_stride, 128)) return rc;
+  if (int rc = make_tile_map(&l.tm_v, p->v, l.is_bf16, p->total_k, p->heads, p->head_dim,
+                             p->v_row_stride, p->v_head_stride, 128)) return rc;
+  FA_CUDA(fa::launch_fwd(l, static_cast<cudaStream_t>(cuda_stream)));
+  return FA_OK;
+}
+
+int fa_debug_dropout_mask(uint8_t* mask_out, int32_t batch_idx, int32_t head_idx,
+                          const fa_fwd_params* p, int32_t seqlen_q, int32_t seqlen_k,
+                          void* cuda_stream) {
+  FA_REQUIRE(p != nullptr && mask_out != nullptr, "null argument");
+  FA_REQUIRE(p->blockmask == nullptr, "block-sparse mask dump is not built yet");
+  fa::KernelArgs a;
+  std::memset(&a, 0, sizeof(a));
+  fill_dropout(p, &a);
+  FA_CUDA(fa::launch_dropout_mask(mask_out, batch_idx, head_idx, a.drop, p->is_causal != 0, seqlen_q,
+                                  seqlen_k, nullptr, 0, 0, static_cast<cudaStream_t>(cuda_stream)));
+  return FA_OK;
+}
+
+size_t fa_bwd_workspace_bytes(int32_t total_q, int32_t heads, int32_t head_dim) {
+  const size_t dpad = head_dim <= 64 ? 64 : 128;
+  return static_cast<size_t>(total_q) * static_cast<size_t>(heads) * dpad * sizeof(float);
+}
+
+int fa_bwd(const fa_bwd_params* p, void* cuda_stream) {
+  (void)p; (void)cuda_stream;
+  return fail(FA_ERR_UNSUPPORTED, "backward is not built yet");
+}
+
+}  // extern "C"

@@ -1,0 +1,101 @@
+// Dropout mask of the reference, reproduced bit for bit.
+//
+// The reference draws its keep/drop decisions from a 7-round Philox4x32 generator
+// (csrc/flash_attn/src/philox.cuh:7-136) whose counter and subsequence are tied to the thread and
+// iteration structure of its sm80 kernels (fmha_fprop_kernel_1xN.h:653-670,
+// fmha/softmax.h:375-414).  Because those are pure functions of (batch, head, row, column), any
+// tiling can regenerate the same bits.  For query row i and key column j of one sequence:
+//
+//   N       key-block size of the reference kernel (128 or 256)
+//   s       = j / N            c16 = (j % N) / 16       o = j % 16       r = i % 16
+//   subsequence = (b*H + h)*256 + (c16 % 8)*32 + (r % 8)*4 + (o % 8)/2
+//   counter     = offset/4 + iter_index(s, i/16) * (N/128) + c16/8
+//   the 128-bit output, read as eight little-endian uint16, is indexed by
+//   slot = (r/8)*4 + (o >= 8 ? 2 : 0) + (o & 1);  keep <=> u16[slot] <= floor(p_keep * 65535)
+//
+// iter_index counts the (key block, 16-row tile) iterations the reference CTA ran before this
+// one, key-block major (see fa_iter_index below).
+#pragma once
+#include <cstdint>
+
+namespace fa {
+
+struct DropoutParams {
+  uint32_t key0, key1;     // seed low / high
+  uint64_t counter_base;   // offset / 4
+  uint32_t threshold;      // floor(p_keep * 65535)
+  int32_t n_shift;         // log2(N): 7 or 8
+  int32_t heads_total;     // H used in the subsequence
+  int32_t head_offset;
+};
+
+__host__ __device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+  const uint64_t p0 = static_cast<uint64_t>(0xD2511F53u) * c[0];
+  const uint64_t p1 = static_cast<uint64_t>(0xCD9E8D57u) * c[2];
+  const uint32_t n0 = static_cast<uint32_t>(p1 >> 32) ^ c[1] ^ k0;
+  const uint32_t n1 = static_cast<uint32_t>(p1);
+  const uint32_t n2 = static_cast<uint32_t>(p0 >> 32) ^ c[3] ^ k1;
+  const uint32_t n3 = static_cast<uint32_t>(p0);
+  c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+}
+
+// Seven rounds: six with a key bump after each, then a final one (philox.cuh:30-42).
+__host__ __device__ __forceinline__ void philox7(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+#pragma unroll
+  for (int i = 0; i < 6; ++i) {
+    philox_round(c, k0, k1);
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  philox_round(c, k0, k1);
+}
+
+// Number of (key block, 16-row tile) iterations the reference ran before (s, i16) for a dense
+// sequence with L = ceil(seqlen_q / 16) row tiles.  Non-causal: every key block walks all L row
+// tiles (fmha_fprop_kernel_1xN.h:365-366).  Causal: key block s starts at row tile s*N/16
+// (:270-272), so the blocks before it ran L, L-u, L-2u ... tiles with u = N/16.
+__host__ __device__ __forceinline__ int64_t fa_iter_index(bool causal, int32_t s, int32_t i16,
+                                                          int32_t L, int32_t n_shift) {
+  if (!causal) return static_cast<int64_t>(s) * L + i16;
+  const int64_t u = static_cast<int64_t>(1) << (n_shift - 4);
+  return static_cast<int64_t>(s) * L - u * (static_cast<int64_t>(s) * (s - 1) / 2) + (i16 - s * u);
+}
+
+// The four keep bits of row i for columns {2q, 2q+1, 2q+8, 2q+9} of the 16-column group that
+// starts at column jg0 (a multiple of 16): one Philox call.  Returned as two 32-bit words, each
+// holding two uint16 random values: w0 -> columns 2q (low half) and 2q+1 (high half),
+// w1 -> columns 2q+8 and 2q+9.
+__host__ __device__ __forceinline__ void fa_dropout_words(const DropoutParams& dp, int64_t bh_sub,
+                                                          int32_t i, int32_t jg0, int32_t q,
+                                                          int64_t iter_index, uint32_t& w0,
+                                                          uint32_t& w1) {
+  const int32_t n_mask = (1 << dp.n_shift) - 1;
+  const int32_t c16 = (jg0 & n_mask) >> 4;
+  const int32_t r = i & 15;
+  const uint64_t subseq = static_cast<uint64_t>(bh_sub) + (c16 & 7) * 32 + (r & 7) * 4 + q;
+  const uint64_t ctr = dp.counter_base + static_cast<uint64_t>(iter_index << (dp.n_shift - 7)) +
+                       static_cast<uint64_t>(c16 >> 3);
+  uint32_t c[4] = {static_cast<uint32_t>(ctr), static_cast<uint32_t>(ctr >> 32),
+                   static_cast<uint32_t>(subseq), static_cast<uint32_t>(subseq >> 32)};
+  philox7(c, dp.key0, dp.key1);
+  if (r >= 8) { w0 = c[2]; w1 = c[3]; } else { w0 = c[0]; w1 = c[1]; }
+}
+
+// 16 keep bits (bit o = column jg0 + o) for row i.
+__host__ __device__ __forceinline__ uint32_t fa_dropout_keep16(const DropoutParams& dp,
+                                                               int64_t bh_sub, int32_t i,
+                                                               int32_t jg0, int64_t iter_index) {
+  uint32_t bits = 0;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint32_t w0, w1;
+    fa_dropout_words(dp, bh_sub, i, jg0, q, iter_index, w0, w1);
+    bits |= ((w0 & 0xFFFFu) <= dp.threshold ? 1u : 0u) << (2 * q);
+    bits |= ((w0 >> 16) <= dp.threshold ? 1u : 0u) << (2 * q + 1);
+    bits |= ((w1 & 0xFFFFu) <= dp.threshold ? 1u : 0u) << (2 * q + 8);
+    bits |= ((w1 >> 16) <= dp.threshold ? 1u : 0u) << (2 * q + 9);
+  }
+  return bits;
+}
+
+}  // namespace fa

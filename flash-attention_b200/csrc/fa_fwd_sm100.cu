@@ -1,0 +1,445 @@
+// FlashAttention forward for sm_100a.
+//
+// One CTA owns two consecutive 128-row query tiles of one (batch, head) pair and walks the key /
+// value sequence in 128-row tiles.  Warp roles:
+//   warps 0-3   softmax group 0 (query tile 0): one thread per query row
+//   warps 4-7   softmax group 1 (query tile 1)
+//   warp  8     TMA producer (Q once, K/V ring)
+//   warp  9     tcgen05.mma issuer
+// Tensor memory (512 columns): S0 [0,128) S1 [128,256) fp32 scores, O0 / O1 fp32 outputs behind
+// them.  The 16-bit probabilities P overwrite the first 64 columns of their S buffer and feed the
+// P*V product straight from tensor memory.
+//
+// Numerics follow the reference forward (csrc/flash_attn/src/fmha_fprop_kernel_1xN.h:365-638):
+// scores in fp32, p = exp2(scale*log2e*(s - max)), row sum of the un-dropped p, P rounded to the
+// 16-bit input type before P*V, O accumulated in fp32 and scaled by 1/(sum * p_keep) at the end,
+// LSE = max*scale + ln(sum), -inf for a row without any valid key.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include "fa_kernels.h"
+#include "sm100_prims.cuh"
+
+namespace fa {
+
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 128;
+constexpr int kFwdThreads = 320;
+
+template <int D>
+struct FwdCfg {
+  static constexpr int kStages = (D == 64) ? 3 : 2;
+  static constexpr int kPanels = D / 64;
+  static constexpr int kTileBytes = kBlockM * D * 2;
+  static constexpr int kSmemBytes = (2 + 2 * kStages) * kTileBytes + 1024;
+  static constexpr uint32_t kTmemS0 = 0, kTmemS1 = 128, kTmemO0 = 256, kTmemO1 = 256 + D;
+};
+
+struct FwdShared {
+  uint64_t q_full[2];
+  uint64_t k_full[3], k_empty[3], v_full[3], v_empty[3];
+  uint64_t s_full[2], p_full[2], o_full[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+template <int D, bool BF16, bool CAUSAL, bool DROPOUT, bool BLOCKSPARSE>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+              const __grid_constant__ CUtensorMap tm_v, const KernelArgs a) {
+  using Cfg = FwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ FwdShared sh;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  const int b = blockIdx.z;
+  const int h = blockIdx.y;
+  const int mp = CAUSAL ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;  // heavy tiles first
+  const int q_start = a.cu_seqlens_q[b];
+  const int sq = a.cu_seqlens_q[b + 1] - q_start;
+  const int k_start = a.cu_seqlens_k[b];
+  const int sk = a.cu_seqlens_k[b + 1] - k_start;
+  if (mp * 2 * kBlockM >= sq) return;
+
+  const int n_kv_total = (sk + kBlockN - 1) / kBlockN;
+  int m0[2], n_tiles[2];
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    m0[g] = (mp * 2 + g) * kBlockM;
+    const bool active = m0[g] < sq;
+    int n = n_kv_total;
+    if (CAUSAL) n = min(n, m0[g] / kBlockN + 1);
+    n_tiles[g] = active ? n : 0;
+  }
+  const int n_max = max(n_tiles[0], n_tiles[1]);
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t smem_q = smem_u32(smem);
+  const uint32_t smem_k = smem_q + 2 * Cfg::kTileBytes;
+  const uint32_t smem_v = smem_k + Cfg::kStages * Cfg::kTileBytes;
+
+  if (tid == 0) {
+    sh.abort_flag = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&sh.q_full[i]), 1);
+      mbar_init(smem_u32(&sh.s_full[i]), 1);
+      mbar_init(smem_u32(&sh.p_full[i]), kBlockM);
+      mbar_init(smem_u32(&sh.o_full[i]), 1);
+    }
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(smem_u32(&sh.k_full[i]), 1);
+      mbar_init(smem_u32(&sh.k_empty[i]), 1);
+      mbar_init(smem_u32(&sh.v_full[i]), 1);
+      mbar_init(smem_u32(&sh.v_empty[i]), 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 8) tmem_alloc(smem_u32(&sh.tmem_base), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh.tmem_base;
+  volatile int* abort_flag = &sh.abort_flag;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      for (int g = 0; g < 2; ++g) {
+        if (n_tiles[g] > 0) {
+          const uint32_t bar = smem_u32(&sh.q_full[g]);
+          mbar_expect_tx(bar, Cfg::kTileBytes);
+          for (int p = 0; p < Cfg::kPanels; ++p)
+            tma_load_3d(smem_q + g * Cfg::kTileBytes + p * 16384, &tm_q, bar, p * 64,
+                        q_start + m0[g], h);
+        }
+      }
+      bool ok = true;
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int s = j % Cfg::kStages;
+        const uint32_t ph = ((j / Cfg::kStages) & 1) ^ 1;
+        if (j >= Cfg::kStages) ok = mbar_wait(smem_u32(&sh.k_empty[s]), ph, abort_flag);
+        if (!ok) break;
+        {
+          const uint32_t bar = smem_u32(&sh.k_full[s]);
+          mbar_expect_tx(bar, Cfg::kTileBytes);
+          for (int p = 0; p < Cfg::kPanels; ++p)
+            tma_load_3d(smem_k + s * Cfg::kTileBytes + p * 16384, &tm_k, bar, p * 64,
+                        k_start + j * kBlockN, h);
+        }
+        if (j >= Cfg::kStages) ok = mbar_wait(smem_u32(&sh.v_empty[s]), ph, abort_flag);
+        if (!ok) break;
+        {
+          const uint32_t bar = smem_u32(&sh.v_full[s]);
+          mbar_expect_tx(bar, Cfg::kTileBytes);
+          for (int p = 0; p < Cfg::kPanels; ++p)
+            tma_load_3d(smem_v + s * Cfg::kTileBytes + p * 16384, &tm_v, bar, p * 64,
+                        k_start + j * kBlockN, h);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc(BF16, false, false, kBlockM, kBlockN);
+      constexpr uint32_t idesc_pv = make_idesc(BF16, false, true, kBlockM, D);
+      const uint32_t tS[2] = {tmem + Cfg::kTmemS0, tmem + Cfg::kTmemS1};
+      const uint32_t tO[2] = {tmem + Cfg::kTmemO0, tmem + Cfg::kTmemO1};
+      auto issue_qk = [&](int g, int stage) {
+        const uint32_t qa = smem_q + g * Cfg::kTileBytes;
+        const uint32_t ka = smem_k + stage * Cfg::kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+          mma_ss(tS[g], make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024),
+                 idesc_qk, ks > 0);
+        }
+        mma_commit(smem_u32(&sh.s_full[g]));
+      };
+      auto issue_pv = [&](int g, int stage, bool accumulate) {
+        const uint32_t va = smem_v + stage * Cfg::kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < kBlockN / 16; ++ks) {
+          mma_ts(tO[g], tS[g] + ks * 8, make_smem_desc(va + ks * 2048, 16384, 1024), idesc_pv,
+                 accumulate || ks > 0);
+        }
+        mma_commit(smem_u32(&sh.o_full[g]));
+      };
+
+      bool ok = true;
+      for (int g = 0; g < 2 && ok; ++g)
+        if (n_tiles[g] > 0) ok = mbar_wait(smem_u32(&sh.q_full[g]), 0, abort_flag);
+      if (ok && n_max > 0) {
+        ok = mbar_wait(smem_u32(&sh.k_full[0]), 0, abort_flag);
+        if (ok) {
+          tc_fence_after();
+          for (int g = 0; g < 2; ++g)
+            if (n_tiles[g] > 0) issue_qk(g, 0);
+          mma_commit(smem_u32(&sh.k_empty[0]));
+        }
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int s = j % Cfg::kStages;
+        const int sn = (j + 1) % Cfg::kStages;
+        const bool has_next = j + 1 < n_max;
+        ok = mbar_wait(smem_u32(&sh.v_full[s]), (j / Cfg::kStages) & 1, abort_flag);
+        if (ok && has_next)
+          ok = mbar_wait(smem_u32(&sh.k_full[sn]), ((j + 1) / Cfg::kStages) & 1, abort_flag);
+        if (!ok) break;
+        for (int g = 0; g < 2; ++g) {
+          if (j < n_tiles[g]) {
+            ok = mbar_wait(smem_u32(&sh.p_full[g]), j & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(g, s, j > 0);
+            if (j + 1 < n_tiles[g]) issue_qk(g, sn);
+          }
+        }
+        if (!ok) break;
+        mma_commit(smem_u32(&sh.v_empty[s]));
+        if (has_next) mma_commit(smem_u32(&sh.k_empty[sn]));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax groups
+    const int g = warp >> 2;
+    const int row = tid & 127;
+    const int ig = m0[g] + row;  // query index within the sequence
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + (g == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1) + lane_sel;
+    const uint32_t tO = tmem + (g == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1) + lane_sel;
+    const int n = n_tiles[g];
+    const bool active = m0[g] < sq;
+
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+
+    // dropout bookkeeping
+    const int64_t bh_sub =
+        (static_cast<int64_t>(b) * a.drop.heads_total + a.drop.head_offset + h) * 256;
+    const int L16 = (sq + 15) >> 4;
+
+    for (int j = 0; j < n && ok; ++j) {
+      ok = mbar_wait(smem_u32(&sh.s_full[g]), j & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sr[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sr[c]);
+      tmem_wait_ld();
+
+      const int col0 = j * kBlockN;
+      bool need_mask = (col0 + kBlockN > sk);
+      if (CAUSAL) need_mask = need_mask || (col0 + kBlockN - 1 > m0[g]);
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = col0 + c * 32 + i;
+            bool valid = col < sk;
+            if (CAUSAL) valid = valid && (col <= ig);
+            if (!valid) sr[c][i] = __float_as_uint(-INFINITY);
+          }
+      }
+      if constexpr (BLOCKSPARSE) {
+        // a 16-row block that is not in the layout for this 256-column key block sees -inf
+        const int kb = col0 >> 8;
+        const int32_t it = a.bs_iter[(static_cast<int64_t>(b) * a.bs_kblocks + kb) * a.bs_rows16 +
+                                     (ig >> 4)];
+        if (it < 0) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) sr[c][i] = __float_as_uint(-INFINITY);
+        }
+      }
+
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[c][i]));
+      const float m_new = fmaxf(m_run, mx);
+
+      if (j > 0) {
+        ok = mbar_wait(smem_u32(&sh.o_full[g]), (j - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const bool grow = m_new > m_run;
+        if (__any_sync(0xffffffffu, grow)) {
+          const float alpha =
+              (m_new == -INFINITY) ? 1.f : fast_exp2((m_run - m_new) * a.scale_log2);
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t orr[32];
+            tmem_ld32(tO + c * 32, orr);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+            tmem_st32(tO + c * 32, orr);
+          }
+          l_run *= alpha;
+        }
+      }
+      m_run = m_new;
+      const float mc = (m_new == -INFINITY) ? 0.f : m_new * a.scale_log2;
+
+      float psum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float p = fast_exp2(fmaf(__uint_as_float(sr[c][i]), a.scale_log2, -mc));
+          psum += p;
+          sr[c][i] = __float_as_uint(p);
+        }
+      l_run += psum;
+
+      if constexpr (DROPOUT) {
+        int64_t it_index;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int hgrp = 0; hgrp < 2; ++hgrp) {
+            const int jg0 = col0 + c * 32 + hgrp * 16;
+            if constexpr (BLOCKSPARSE) {
+              it_index = a.bs_iter[(static_cast<int64_t>(b) * a.bs_kblocks + (jg0 >> 8)) *
+                                       a.bs_rows16 + (ig >> 4)];
+            } else {
+              it_index = fa_iter_index(CAUSAL, jg0 >> a.drop.n_shift, ig >> 4, L16, a.drop.n_shift);
+            }
+            const uint32_t keep = fa_dropout_keep16(a.drop, bh_sub, ig, jg0, it_index);
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (!((keep >> i) & 1u)) sr[c][hgrp * 16 + i] = 0u;
+          }
+      }
+
+      // pack to 16 bit and hand P to the tensor core through tensor memory
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pr[32];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          pr[i] = pack2<BF16>(__uint_as_float(sr[2 * c][2 * i]), __uint_as_float(sr[2 * c][2 * i + 1]));
+          pr[16 + i] = pack2<BF16>(__uint_as_float(sr[2 * c + 1][2 * i]),
+                                   __uint_as_float(sr[2 * c + 1][2 * i + 1]));
+        }
+        tmem_st32(tS + c * 32, pr);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sh.p_full[g]));
+    }
+
+    // ---------------- epilogue: O = acc / (sum * p_keep), LSE
+    if (active) {
+      if (n > 0 && ok) {
+        ok = mbar_wait(smem_u32(&sh.o_full[g]), (n - 1) & 1, abort_flag);
+        tc_fence_after();
+      }
+      const bool bad_sum = (l_run == 0.f) || (l_run != l_run);
+      const float inv = bad_sum ? 1.f : (1.f / l_run) * a.rp_keep;
+      const bool store_row = ok && (ig < sq);
+      uint16_t* orow = reinterpret_cast<uint16_t*>(a.o) +
+                       static_cast<int64_t>(q_start + ig) * a.o_row_stride +
+                       static_cast<int64_t>(h) * a.o_head_stride;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t orr[32];
+        if (n > 0 && ok) {
+          tmem_ld32(tO + c * 32, orr);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) orr[i] = 0u;
+        }
+        if (store_row && c * 32 < a.head_dim) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            pk[i] = pack2<BF16>(__uint_as_float(orr[2 * i]) * inv, __uint_as_float(orr[2 * i + 1]) * inv);
+          uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+          const int nvec = min(4, (a.head_dim - c * 32) / 8);
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            if (v < nvec) dst[v] = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+        }
+      }
+      if (store_row) {
+        const float lse = bad_sum ? -INFINITY : (m_run * a.scale + __logf(l_run));
+        a.lse[(static_cast<int64_t>(b) * a.heads + h) * a.lse_stride + ig] = lse;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tmem_dealloc(tmem, 512);
+    if (lane == 0 && sh.abort_flag && a.status) atomicExch(a.status, 1);
+  }
+}
+
+template <int D, bool BF16, bool CAUSAL, bool DROPOUT, bool BS>
+cudaError_t launch_one(const FwdLaunch& l, cudaStream_t stream) {
+  auto kernel = fa_fwd_kernel<D, BF16, CAUSAL, DROPOUT, BS>;
+  constexpr int smem = FwdCfg<D>::kSmemBytes;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  dim3 grid((l.max_seqlen_q + 2 * kBlockM - 1) / (2 * kBlockM), l.args.heads, l.args.batch);
+  kernel<<<grid, kFwdThreads, smem, stream>>>(l.tm_q, l.tm_k, l.tm_v, l.args);
+  return cudaGetLastError();
+}
+
+template <int D, bool BF16, bool CAUSAL>
+cudaError_t launch_dd(const FwdLaunch& l, cudaStream_t stream) {
+  const bool bs = l.args.bs_iter != nullptr;
+  if (l.is_dropout) {
+    return bs ? launch_one<D, BF16, CAUSAL, true, true>(l, stream)
+              : launch_one<D, BF16, CAUSAL, true, false>(l, stream);
+  }
+  return bs ? launch_one<D, BF16, CAUSAL, false, true>(l, stream)
+            : launch_one<D, BF16, CAUSAL, false, false>(l, stream);
+}
+
+template <int D>
+cudaError_t launch_d(const FwdLaunch& l, cudaStream_t stream) {
+  if (l.is_bf16) {
+    return l.is_causal ? launch_dd<D, true, true>(l, stream) : launch_dd<D, true, false>(l, stream);
+  }
+  return l.is_causal ? launch_dd<D, false, true>(l, stream) : launch_dd<D, false, false>(l, stream);
+}
+
+}  // namespace
+
+cudaError_t launch_fwd(const FwdLaunch& l, cudaStream_t stream) {
+  return l.dpad == 64 ? launch_d<64>(l, stream) : launch_d<128>(l, stream);
+}
+
+}  // namespace fa

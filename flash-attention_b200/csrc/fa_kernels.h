@@ -1,0 +1,58 @@
+// Host-side launch interface between the C ABI (fa_api.cu) and the kernel translation units.
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include "fa_dropout.cuh"
+
+namespace fa {
+
+// Arguments shared by the forward and backward kernels (device pointers, sizes in elements).
+struct KernelArgs {
+  const int32_t* cu_seqlens_q;
+  const int32_t* cu_seqlens_k;
+  // Block-sparse: per (batch, key block of 256, 16-row block) iteration index of the reference
+  // kernel, or -1 when the block is not in the layout; nullptr for dense attention.
+  const int32_t* bs_iter;
+  int32_t bs_rows16;   // row length of bs_iter: 16-row blocks per key block
+  int32_t bs_kblocks;  // key blocks (of 256) per batch entry in bs_iter
+  void* o;
+  float* lse;
+  int64_t o_row_stride, o_head_stride;
+  int64_t lse_stride;
+  int32_t batch, heads, head_dim;
+  float scale;        // softmax_scale
+  float scale_log2;   // softmax_scale * log2(e)
+  float rp_keep;      // 1 / p_keep
+  DropoutParams drop;
+  int32_t* status;
+};
+
+struct BwdArgs {
+  KernelArgs k;
+  const void* q; const void* kk; const void* v;       // raw pointers for the plain-load paths
+  const void* o_in; const void* dout;
+  int64_t q_row_stride, q_head_stride;
+  int64_t do_row_stride, do_head_stride;
+  void* dq; void* dk; void* dv;
+  int64_t dq_row_stride, dq_head_stride, dk_row_stride, dk_head_stride, dv_row_stride, dv_head_stride;
+  float* softmax_d;
+  float* dq_accum;    // fp32 [total_q, heads, Dpad]
+  int32_t total_q, total_k, max_seqlen_q, max_seqlen_k;
+  float p_keep;
+};
+
+struct FwdLaunch {
+  CUtensorMap tm_q, tm_k, tm_v;
+  KernelArgs args;
+  int32_t max_seqlen_q, max_seqlen_k;
+  bool is_bf16, is_causal, is_dropout;
+  int32_t dpad;  // 64 or 128
+};
+
+cudaError_t launch_fwd(const FwdLaunch& l, cudaStream_t stream);
+cudaError_t launch_dropout_mask(uint8_t* out, int b, int h, const DropoutParams& dp, bool causal,
+                                int sq, int sk, const int32_t* bs_iter, int bs_kblocks,
+                                int bs_rows16, cudaStream_t stream);
+
+}  // namespace fa

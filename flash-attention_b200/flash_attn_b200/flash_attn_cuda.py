@@ -1,0 +1,134 @@
+"""Drop-in for the reference's compiled extension module `flash_attn_cuda`
+(csrc/flash_attn/fmha_api.cpp:721-727): `fwd`, `bwd`, `fwd_block`, `bwd_block` with the reference's
+argument lists, implemented as a thin binding over the C ABI of libfa_b200.so.
+
+PyTorch is used here only for device memory (output / scratch allocation through the caching
+allocator), the current stream and the default CUDA generator's Philox state.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import BwdParams, FwdParams, check, lib
+
+_status = {}
+
+
+def _status_buffer(device):
+    """Per-device int32[4] the kernels write to when they abandon a bounded wait."""
+    buf = _status.get(device)
+    if buf is None:
+        buf = torch.zeros(4, dtype=torch.int32, device=device)
+        _status[device] = buf
+    return buf
+
+
+def check_device_status(device=None):
+    """Synchronises and raises if any kernel on `device` reported an abandoned wait."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    buf = _status.get(device)
+    if buf is None:
+        return
+    val = buf.cpu().tolist()
+    if any(val):
+        buf.zero_()
+        raise RuntimeError("fa_b200: a kernel abandoned a bounded wait (status %s)" % val)
+
+
+def _require(cond, msg):
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _philox_state(gen, increment):
+    """(seed, offset) of the generator, then advance it by `increment` -- what
+    CUDAGeneratorImpl::philox_cuda_state(increment) does in the reference
+    (csrc/flash_attn/fmha_api.cpp:288-292)."""
+    if gen is None:
+        gen = torch.cuda.default_generators[torch.cuda.current_device()]
+    seed = gen.initial_seed()
+    offset = gen.get_offset()
+    # the generator keeps its offset a multiple of 4, like the reference's PhiloxCudaState
+    gen.set_offset(offset + ((int(increment) + 3) // 4) * 4)
+    return seed, offset
+
+
+def _check_qkv(q, k, v, cu_seqlens_q, cu_seqlens_k):
+    _require(q.is_cuda and k.is_cuda and v.is_cuda, "q, k, v must be CUDA tensors")
+    _require(q.dtype in (torch.float16, torch.bfloat16), "q must be fp16 or bf16")
+    _require(k.dtype == q.dtype and v.dtype == q.dtype, "q, k, v must have the same dtype")
+    _require(cu_seqlens_q.dtype == torch.int32 and cu_seqlens_k.dtype == torch.int32,
+             "cu_seqlens must be int32")
+    _require(cu_seqlens_q.is_cuda and cu_seqlens_k.is_cuda, "cu_seqlens must be CUDA tensors")
+    _require(cu_seqlens_q.is_contiguous() and cu_seqlens_k.is_contiguous(),
+             "cu_seqlens must be contiguous")
+    _require(q.dim() == 3 and k.dim() == 3 and v.dim() == 3, "q, k, v must be (total, heads, d)")
+    _require(q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1,
+             "q, k, v must have a contiguous last dimension")
+    batch = cu_seqlens_q.numel() - 1
+    _require(batch > 0, "batch size must be positive")
+    _require(cu_seqlens_k.numel() == batch + 1, "cu_seqlens_q / cu_seqlens_k size mismatch")
+    total_q, heads, d = q.shape
+    total_k = k.shape[0]
+    _require(d in (16, 32, 64, 128), "head_dim must be 16, 32, 64 or 128")
+    _require(tuple(k.shape) == (total_k, heads, d), "k has the wrong shape")
+    _require(tuple(v.shape) == (total_k, heads, d), "v has the wrong shape")
+    return batch, total_q, total_k, heads, d
+
+
+def _fill_fwd(p, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout, scale, causal,
+              seed, offset):
+    batch, total_q, total_k, heads, d = _check_qkv(q, k, v, cu_q, cu_k)
+    p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    p.o = o.data_ptr()
+    p.softmax_lse = lse.data_ptr()
+    p.cu_seqlens_q, p.cu_seqlens_k = cu_q.data_ptr(), cu_k.data_ptr()
+    p.blockmask = None
+    p.s_dmask = None
+    p.q_row_stride, p.q_head_stride = q.stride(0), q.stride(1)
+    p.k_row_stride, p.k_head_stride = k.stride(0), k.stride(1)
+    p.v_row_stride, p.v_head_stride = v.stride(0), v.stride(1)
+    p.o_row_stride, p.o_head_stride = o.stride(0), o.stride(1)
+    p.lse_stride = lse.shape[-1]
+    p.batch, p.heads, p.head_dim = batch, heads, d
+    p.total_q, p.total_k = total_q, total_k
+    p.max_seqlen_q, p.max_seqlen_k = int(max_q), int(max_k)
+    p.p_dropout = float(p_dropout)
+    p.softmax_scale = float(scale)
+    p.is_causal = int(bool(causal))
+    p.is_bf16 = int(q.dtype == torch.bfloat16)
+    p.philox_seed, p.philox_offset = seed, offset
+    p.mask_heads_total, p.mask_head_offset = 0, 0
+    p.status = _status_buffer(q.device).data_ptr()
+
+
+def _round_up(x, m):
+    return (x + m - 1) // m * m
+
+
+def fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale,
+        zero_tensors, is_causal, return_softmax, gen=None):
+    """mha_fwd (csrc/flash_attn/fmha_api.cpp:173-299): returns [o, softmax_lse(, s)]."""
+    batch, total_q, total_k, heads, d = _check_qkv(q, k, v, cu_seqlens_q, cu_seqlens_k)
+    _require(p_dropout < 1.0, "p_dropout must be < 1")
+    if return_softmax:
+        raise RuntimeError("fa_b200: return_softmax is not available")
+    with torch.cuda.device(q.device):
+        lse_len = _round_up(int(max_seqlen_q), 16)
+        if zero_tensors:
+            o = torch.zeros((total_q, heads, d), dtype=q.dtype, device=q.device)
+            lse = torch.full((batch, heads, lse_len), float("-inf"), dtype=torch.float32,
+                             device=q.device)
+        else:
+            o = torch.empty((total_q, heads, d), dtype=q.dtype, device=q.device)
+            lse = torch.empty((batch, heads, lse_len), dtype=torch.float32, device=q.device)
+        seed, offset = 0, 0
+        if p_dropout > 0:
+            inc = lib.fa_philox_increment(d, int(max_seqlen_q), int(max_seqlen_k), 0)
+            seed, offset = _philox_state(gen, inc)
+        p = FwdParams()
+        _fill_fwd(p, q, k, v, o, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+                  p_dropout, softmax_scale, is_causal, seed, offset)
+        check(lib.fa_fwd(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return [o, lse]

@@ -1,0 +1,132 @@
+/*
+ * C ABI of libfa_b200.so: FlashAttention forward / backward for NVIDIA B200 (sm_100a).
+ *
+ * The entry points replace the host functions of the reference extension
+ * (csrc/flash_attn/fmha_api.cpp): the same argument contract, expressed as plain pointers and
+ * sizes so that any binding (pybind11, ctypes, cgo, JNI ...) can call it.  Nothing here
+ * allocates output tensors: the caller owns every buffer.  All launches are asynchronous on the
+ * stream that is passed in; no entry point synchronises.
+ *
+ * Tensor layouts (identical to the reference, fmha_api.cpp:173-186):
+ *   q            [total_q, heads, head_dim]   16-bit (fp16 or bf16), last dim contiguous,
+ *   k, v         [total_k, heads, head_dim]   row / head strides given in elements
+ *   cu_seqlens_* [batch + 1] int32            cumulative sequence lengths (varlen packing)
+ *   o            [total_q, heads, head_dim]
+ *   softmax_lse  [batch, heads, lse_stride]   fp32, natural-log LSE of the scaled scores
+ *
+ * Every function returns FA_OK (0) or a negative FA_ERR_* code; fa_status_string() names it and
+ * fa_last_error() returns a thread-local detail message.
+ */
+#ifndef FA_B200_H_
+#define FA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FA_OK 0
+#define FA_ERR_INVALID_ARGUMENT (-1) /* shape / stride / dtype / alignment the kernels cannot take */
+#define FA_ERR_CUDA (-2)             /* a CUDA runtime or driver call failed                        */
+#define FA_ERR_UNSUPPORTED (-3)      /* valid in the reference but not built here                    */
+#define FA_ERR_WORKSPACE (-4)        /* workspace missing or too small                               */
+
+/* Forward arguments: replaces FMHA_fprop_params (csrc/flash_attn/src/fmha.h:50-139) as filled by
+ * set_params_fprop (csrc/flash_attn/fmha_api.cpp:37-117). */
+typedef struct fa_fwd_params {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* softmax_lse;
+  const int32_t* cu_seqlens_q;
+  const int32_t* cu_seqlens_k;
+  /* Block-sparse only (fmha_api.cpp:451-573): converted block mask [max_seqlen_k_rounded/256,
+   * max_seqlen_q_rounded/16] int32 as produced by convert_blockmask; NULL for dense attention. */
+  const int32_t* blockmask;
+  /* Optional [batch, heads, s_rows, s_cols] 16-bit output of the softmax probabilities with the
+   * sign bit marking dropped entries (return_softmax); NULL to skip. */
+  void* s_dmask;
+  int64_t s_rows, s_cols;
+  /* strides in elements */
+  int64_t q_row_stride, q_head_stride;
+  int64_t k_row_stride, k_head_stride;
+  int64_t v_row_stride, v_head_stride;
+  int64_t o_row_stride, o_head_stride;
+  int64_t lse_stride; /* row length of softmax_lse, >= max_seqlen_q */
+  int32_t batch, heads, head_dim;
+  int32_t total_q, total_k;
+  int32_t max_seqlen_q, max_seqlen_k; /* as passed by the caller, un-rounded */
+  float p_dropout;                    /* probability of dropping, in [0, 1) */
+  float softmax_scale;
+  int32_t is_causal;
+  int32_t is_bf16; /* 0 = fp16, 1 = bf16 */
+  /* Philox state (seed, offset) exactly as at::cuda::philox::unpack returns it in the reference
+   * (fmha_fprop_kernel_1xN.h:653-656); ignored when p_dropout == 0. */
+  uint64_t philox_seed, philox_offset;
+  /* Head count / first head used in the Philox subsequence, for callers that shard heads across
+   * devices and want the mask of the unsharded call.  0 / 0 means (heads, 0). */
+  int32_t mask_heads_total, mask_head_offset;
+  /* Optional device int32[4]: a kernel that abandons a bounded wait writes a non-zero code here. */
+  int32_t* status;
+} fa_fwd_params;
+
+/* Backward arguments: replaces FMHA_dgrad_params (csrc/flash_attn/src/fmha.h:141-163) as filled
+ * by set_params_dgrad (csrc/flash_attn/fmha_api.cpp:119-171). */
+typedef struct fa_bwd_params {
+  fa_fwd_params fwd; /* q, k, v, o (read), softmax_lse (read), strides, sizes, flags, philox */
+  const void* dout;  /* [total_q, heads, head_dim], contiguous */
+  void* dq;          /* written in place, caller owned, strides below */
+  void* dk;
+  void* dv;
+  float* softmax_d; /* [batch, heads, lse_stride] fp32 out: p_keep * rowsum(dO * O) */
+  int64_t dq_row_stride, dq_head_stride;
+  int64_t dk_row_stride, dk_head_stride;
+  int64_t dv_row_stride, dv_head_stride;
+  /* Scratch of at least fa_bwd_workspace_bytes(): fp32 dQ accumulator.  Contents on entry are
+   * ignored; the call clears what it needs. */
+  void* workspace;
+  size_t workspace_bytes;
+} fa_bwd_params;
+
+/* mha_fwd (csrc/flash_attn/fmha_api.cpp:173-299) and, with blockmask != NULL, mha_fwd_block
+ * (:451-573).  Writes o and softmax_lse. */
+int fa_fwd(const fa_fwd_params* params, void* cuda_stream);
+
+/* mha_bwd (csrc/flash_attn/fmha_api.cpp:302-449) and, with blockmask != NULL, mha_bwd_block
+ * (:575-718).  Writes dq, dk, dv and softmax_d. */
+int fa_bwd(const fa_bwd_params* params, void* cuda_stream);
+
+/* Size of the scratch fa_bwd needs: replaces the dq_tmp allocation of mha_bwd
+ * (csrc/flash_attn/fmha_api.cpp:402-404). */
+size_t fa_bwd_workspace_bytes(int32_t total_q, int32_t heads, int32_t head_dim);
+
+/* Generator increment the caller must apply after a forward with dropout: replaces the
+ * counter_offset computed in run_fmha_fp16_sm80_loop_ (fmha_fprop_fp16_kernel.sm80.cu:44-54). */
+uint64_t fa_philox_increment(int32_t head_dim, int32_t max_seqlen_q, int32_t max_seqlen_k,
+                             int32_t is_blocksparse);
+
+/* Key-block size N that fixes the dropout-mask layout: the block-size rule of mha_fwd for an
+ * sm80 device (csrc/flash_attn/fmha_api.cpp:232-239 with fmha_fprop_fp16_kernel.sm80.cu:84-146). */
+int32_t fa_mask_block_n(int32_t head_dim, int32_t max_seqlen_k, int32_t is_blocksparse);
+
+/* Writes the dropout keep-mask (1 = kept) of one (batch, head) pair into a device uint8
+ * [seqlen_q, seqlen_k] buffer using the same device code as the attention kernels; test hook
+ * standing in for the sign bits of the reference's S_dmask output
+ * (csrc/flash_attn/src/fmha/gmem_tile.h:289-405). */
+int fa_debug_dropout_mask(uint8_t* mask_out, int32_t batch_idx, int32_t head_idx,
+                          const fa_fwd_params* params, int32_t seqlen_q, int32_t seqlen_k,
+                          void* cuda_stream);
+
+const char* fa_status_string(int status);
+const char* fa_last_error(void);
+
+/* 0 when the current device is an sm_100 part and the library can run on it. */
+int fa_device_supported(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H_ */
