@@ -223,8 +223,55 @@ size_t fa_bwd_workspace_bytes(int32_t total_q, int32_t heads, int32_t head_dim) 
 }
 
 int fa_bwd(const fa_bwd_params* p, void* cuda_stream) {
-  (void)p; (void)cuda_stream;
-  return fail(FA_ERR_UNSUPPORTED, "backward is not built yet");
+  FA_REQUIRE(p != nullptr, "params is null");
+  const fa_fwd_params* f = &p->fwd;
+  if (int rc = validate_common(f)) return rc;
+  FA_REQUIRE(f->o && f->softmax_lse, "out and softmax_lse must be non-null");
+  FA_REQUIRE(p->dout && p->dq && p->dk && p->dv && p->softmax_d, "dout, dq, dk, dv, softmax_d must be non-null");
+  FA_REQUIRE(((reinterpret_cast<uintptr_t>(p->dq) | reinterpret_cast<uintptr_t>(p->dk) |
+               reinterpret_cast<uintptr_t>(p->dv) | reinterpret_cast<uintptr_t>(f->o)) & 15) == 0,
+             "o, dq, dk, dv must be 16-byte aligned");
+  FA_REQUIRE(p->dq_row_stride % 8 == 0 && p->dq_head_stride % 8 == 0 && p->dk_row_stride % 8 == 0 &&
+                 p->dk_head_stride % 8 == 0 && p->dv_row_stride % 8 == 0 && p->dv_head_stride % 8 == 0 &&
+                 f->o_row_stride % 8 == 0 && f->o_head_stride % 8 == 0,
+             "gradient strides must be multiples of 8 elements");
+  if (f->blockmask) return fail(FA_ERR_UNSUPPORTED, "block-sparse backward is not built yet");
+  const size_t need = fa_bwd_workspace_bytes(f->total_q, f->heads, f->head_dim);
+  if (p->workspace == nullptr || p->workspace_bytes < need)
+    return fail(FA_ERR_WORKSPACE, "workspace must hold " + std::to_string(need) + " bytes");
+  FA_REQUIRE((reinterpret_cast<uintptr_t>(p->workspace) & 15) == 0, "workspace must be 16-byte aligned");
+
+  fa::BwdLaunch l;
+  std::memset(&l, 0, sizeof(l));
+  fill_args(f, &l.args.k);
+  l.dpad = f->head_dim <= 64 ? 64 : 128;
+  l.is_bf16 = f->is_bf16 != 0;
+  l.is_causal = f->is_causal != 0;
+  l.is_dropout = f->p_dropout > 0.f;
+  fa::BwdArgs& a = l.args;
+  a.o_in = f->o;
+  a.dout = p->dout;
+  a.do_row_stride = static_cast<int64_t>(f->heads) * f->head_dim;
+  a.do_head_stride = f->head_dim;
+  a.dq = p->dq; a.dk = p->dk; a.dv = p->dv;
+  a.dq_row_stride = p->dq_row_stride; a.dq_head_stride = p->dq_head_stride;
+  a.dk_row_stride = p->dk_row_stride; a.dk_head_stride = p->dk_head_stride;
+  a.dv_row_stride = p->dv_row_stride; a.dv_head_stride = p->dv_head_stride;
+  a.softmax_d = p->softmax_d;
+  a.dq_accum = static_cast<float*>(p->workspace);
+  a.total_q = f->total_q; a.total_k = f->total_k;
+  a.max_seqlen_q = f->max_seqlen_q; a.max_seqlen_k = f->max_seqlen_k;
+  a.p_keep = 1.f - f->p_dropout;
+  if (int rc = make_tile_map(&l.tm_q, f->q, l.is_bf16, f->total_q, f->heads, f->head_dim,
+                             f->q_row_stride, f->q_head_stride, 128)) return rc;
+  if (int rc = make_tile_map(&l.tm_k, f->k, l.is_bf16, f->total_k, f->heads, f->head_dim,
+                             f->k_row_stride, f->k_head_stride, 128)) return rc;
+  if (int rc = make_tile_map(&l.tm_v, f->v, l.is_bf16, f->total_k, f->heads, f->head_dim,
+                             f->v_row_stride, f->v_head_stride, 128)) return rc;
+  if (int rc = make_tile_map(&l.tm_do, p->dout, l.is_bf16, f->total_q, f->heads, f->head_dim,
+                             a.do_row_stride, a.do_head_stride, 128)) return rc;
+  FA_CUDA(fa::launch_bwd(l, static_cast<cudaStream_t>(cuda_stream)));
+  return FA_OK;
 }
 
 }  // extern "C"

@@ -1,0 +1,610 @@
+// FlashAttention backward for sm_100a.
+//
+// Three launches:
+//   1. bwd_preprocess: softmax_d[b,h,i] = p_keep * sum_d dO*O and zero-fill of the fp32 dQ
+//      accumulator (HBM bound).
+//   2. bwd_main: one CTA per 128-row key/value tile of one (batch, head) pair; it keeps K and V in
+//      shared memory and walks the 128-row query tiles.  Per tile pair it recomputes
+//      S = Q K^T and dP = dO V^T on the tensor cores (accumulators in tensor memory), forms
+//      P = exp2(scale*log2e*S - LSE*log2e), regenerates the dropout mask, forms
+//      dS = P*(dP - D) (kept) or -P*D (dropped), writes the 16-bit P~ and dS to shared memory
+//      and issues dV += P~^T dO, dK += dS^T Q, dQ = dS K.  dQ tiles are added into the fp32
+//      accumulator with vector reductions; dK and dV stay in tensor memory until the end.
+//   3. bwd_postprocess: dq = accumulator * scale / p_keep in the 16-bit output type.
+//
+// The formulas are those of the reference backward
+// (csrc/flash_attn/src/fmha_dgrad_kernel_1xN_loop.h:304-661): P recomputed from the saved LSE
+// (:333), dropped entries contribute -P*D (:402-418), dQ and dK scaled by scale/p_keep (:583,
+// :628), dV by 1/p_keep (:613-619), P~ and dS rounded to the 16-bit type before their products.
+//
+// Warp roles in bwd_main (384 threads):
+//   warps 0-3   compute group: S, dP -> P~, dS (one thread per query row), dV epilogue
+//   warps 4-7   dQ group: tensor memory -> global reductions, dK epilogue
+//   warp  8     TMA producer          warp 9   tcgen05.mma issuer          warps 10-11 idle
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include "fa_kernels.h"
+#include "sm100_prims.cuh"
+
+namespace fa {
+
+namespace {
+
+constexpr int kBM = 128;  // query rows per tile
+constexpr int kBN = 128;  // key rows per tile
+constexpr int kBwdThreads = 384;
+
+template <int D>
+struct BwdCfg {
+  static constexpr int kQStages = (D == 64) ? 2 : 1;
+  static constexpr bool kAliasDq = (D == 128);  // dQ shares tensor-memory columns with dP
+  static constexpr int kTileBytes = 128 * D * 2;
+  static constexpr int kPdsBytes = 128 * 128 * 2;
+  // K, V, (Q, dO) x stages, P~, dS
+  static constexpr int kSmemBytes = (2 + 2 * kQStages) * kTileBytes + 2 * kPdsBytes + 1024;
+  static constexpr uint32_t kTmemS = 0, kTmemDP = 128, kTmemDV = 256, kTmemDK = 256 + D;
+  static constexpr uint32_t kTmemDQ = kAliasDq ? 128 : 256 + 2 * D;
+};
+
+struct BwdShared {
+  uint64_t kv_full;
+  uint64_t q_full[2], q_empty[2];
+  uint64_t sdp_full, sdp_consumed, pds_ready, pds_free, dq_full, dq_consumed;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  if constexpr (BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
+}
+
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// ------------------------------------------------------------------------------------------------
+template <int D, bool BF16, bool CAUSAL, bool DROPOUT, bool BLOCKSPARSE>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+              const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+              const BwdArgs a) {
+  using Cfg = BwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ BwdShared sh;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int b = blockIdx.z;
+  const int h = blockIdx.y;
+  const int nt = blockIdx.x;  // key tile
+  const KernelArgs& ka = a.k;
+
+  const int q_start = ka.cu_seqlens_q[b];
+  const int sq = ka.cu_seqlens_q[b + 1] - q_start;
+  const int k_start = ka.cu_seqlens_k[b];
+  const int sk = ka.cu_seqlens_k[b + 1] - k_start;
+  const int n0 = nt * kBN;
+  if (n0 >= sk) return;
+
+  const int m_tiles = (sq + kBM - 1) / kBM;
+  const int m_begin = CAUSAL ? min(m_tiles, n0 / kBM) : 0;
+  const int nm = m_tiles - m_begin;
+
+  uint16_t* dk_base = reinterpret_cast<uint16_t*>(a.dk);
+  uint16_t* dv_base = reinterpret_cast<uint16_t*>(a.dv);
+
+  if (nm <= 0) {
+    // no query row sees these keys: their gradients are zero
+    for (int idx = tid; idx < kBN * (ka.head_dim / 8); idx += kBwdThreads) {
+      const int r = idx / (ka.head_dim / 8), c = (idx % (ka.head_dim / 8)) * 8;
+      if (n0 + r < sk) {
+        const int64_t row = k_start + n0 + r;
+        *reinterpret_cast<uint4*>(dk_base + row * a.dk_row_stride + h * a.dk_head_stride + c) =
+            make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(dv_base + row * a.dv_row_stride + h * a.dv_head_stride + c) =
+            make_uint4(0, 0, 0, 0);
+      }
+    }
+    return;
+  }
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t smem_k = smem_u32(smem);
+  const uint32_t smem_v = smem_k + Cfg::kTileBytes;
+  const uint32_t smem_q = smem_v + Cfg::kTileBytes;                       // stages of Q
+  const uint32_t smem_do = smem_q + Cfg::kQStages * Cfg::kTileBytes;      // stages of dO
+  const uint32_t smem_p = smem_do + Cfg::kQStages * Cfg::kTileBytes;
+  const uint32_t smem_ds = smem_p + Cfg::kPdsBytes;
+  uint8_t* p_ptr = smem + (2 + 2 * Cfg::kQStages) * Cfg::kTileBytes;
+  uint8_t* ds_ptr = p_ptr + Cfg::kPdsBytes;
+
+  if (tid == 0) {
+    sh.abort_flag = 0;
+    mbar_init(smem_u32(&sh.kv_full), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&sh.q_full[i]), 1);
+      mbar_init(smem_u32(&sh.q_empty[i]), 1);
+    }
+    mbar_init(smem_u32(&sh.sdp_full), 1);
+    mbar_init(smem_u32(&sh.sdp_consumed), kBM);
+    mbar_init(smem_u32(&sh.pds_ready), kBM);
+    mbar_init(smem_u32(&sh.pds_free), 1);
+    mbar_init(smem_u32(&sh.dq_full), 1);
+    mbar_init(smem_u32(&sh.dq_consumed), kBM);
+    fence_mbar_init();
+  }
+  if (warp == 8) tmem_alloc(smem_u32(&sh.tmem_base), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh.tmem_base;
+  volatile int* abort_flag = &sh.abort_flag;
+
+  const float rp_keep = ka.rp_keep;
+
+  if (warp >= 8) {
+    reg_dealloc<40>();
+    if (warp == 8 && lane == 0) {
+      // -------------------------------------------------------------- TMA producer
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      tma_prefetch_desc(&tm_do);
+      {
+        const uint32_t bar = smem_u32(&sh.kv_full);
+        mbar_expect_tx(bar, 2 * Cfg::kTileBytes);
+        for (int p = 0; p < D / 64; ++p) {
+          tma_load_3d(smem_k + p * 16384, &tm_k, bar, p * 64, k_start + n0, h);
+          tma_load_3d(smem_v + p * 16384, &tm_v, bar, p * 64, k_start + n0, h);
+        }
+      }
+      bool ok = true;
+      for (int t = 0; t < nm && ok; ++t) {
+        const int s = t % Cfg::kQStages;
+        if (t >= Cfg::kQStages)
+          ok = mbar_wait(smem_u32(&sh.q_empty[s]), ((t / Cfg::kQStages) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        const uint32_t bar = smem_u32(&sh.q_full[s]);
+        mbar_expect_tx(bar, 2 * Cfg::kTileBytes);
+        const int row = q_start + (m_begin + t) * kBM;
+        for (int p = 0; p < D / 64; ++p) {
+          tma_load_3d(smem_q + s * Cfg::kTileBytes + p * 16384, &tm_q, bar, p * 64, row, h);
+          tma_load_3d(smem_do + s * Cfg::kTileBytes + p * 16384, &tm_do, bar, p * 64, row, h);
+        }
+      }
+    } else if (warp == 9 && lane == 0) {
+      // -------------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc_s = make_idesc(BF16, false, false, 128, 128);   // Q K^T, dO V^T
+      constexpr uint32_t idesc_tt = make_idesc(BF16, true, true, 128, D);      // P~^T dO, dS^T Q
+      constexpr uint32_t idesc_dq = make_idesc(BF16, false, true, 128, D);     // dS K
+      const uint32_t tS = tmem + Cfg::kTmemS, tDP = tmem + Cfg::kTmemDP;
+      const uint32_t tDV = tmem + Cfg::kTmemDV, tDK = tmem + Cfg::kTmemDK, tDQ = tmem + Cfg::kTmemDQ;
+
+      auto issue_kk = [&](uint32_t dst, uint32_t a_base, uint32_t b_base) {  // both K-major, K = D
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+          mma_ss(dst, make_smem_desc(a_base + off, 16, 1024), make_smem_desc(b_base + off, 16, 1024),
+                 idesc_s, ks > 0);
+        }
+      };
+      auto issue_tt = [&](uint32_t dst, uint32_t a_base, uint32_t b_base, bool acc) {
+        // A = [q][kv] read as M = kv (MN-major); B = [q][d] read as N = d (MN-major); K = q rows
+#pragma unroll
+        for (int ks = 0; ks < kBM / 16; ++ks) {
+          mma_ss(dst, make_smem_desc(a_base + ks * 2048, 16384, 1024),
+                 make_smem_desc(b_base + ks * 2048, 16384, 1024), idesc_tt, acc || ks > 0);
+        }
+      };
+      auto issue_dq = [&](uint32_t dst, uint32_t a_base, uint32_t b_base) {
+        // A = dS [q][kv] K-major; B = K [kv][d] read as N = d (MN-major); K = kv
+#pragma unroll
+        for (int ks = 0; ks < kBN / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+          mma_ss(dst, make_smem_desc(a_base + off, 16, 1024),
+                 make_smem_desc(b_base + ks * 2048, 16384, 1024), idesc_dq, ks > 0);
+        }
+      };
+
+      bool ok = mbar_wait(smem_u32(&sh.kv_full), 0, abort_flag);
+      if (ok) ok = mbar_wait(smem_u32(&sh.q_full[0]), 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_kk(tS, smem_q, smem_k);
+        issue_kk(tDP, smem_do, smem_v);
+        mma_commit(smem_u32(&sh.sdp_full));
+      }
+      for (int t = 0; t < nm && ok; ++t) {
+        const int s = t % Cfg::kQStages;
+        const bool has_next = t + 1 < nm;
+        const int sn = (t + 1) % Cfg::kQStages;
+        if (Cfg::kQStages > 1 && has_next) {
+          ok = mbar_wait(smem_u32(&sh.q_full[sn]), ((t + 1) / Cfg::kQStages) & 1, abort_flag);
+          if (ok) ok = mbar_wait(smem_u32(&sh.sdp_consumed), t & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_kk(tS, smem_q + sn * Cfg::kTileBytes, smem_k);
+          issue_kk(tDP, smem_do + sn * Cfg::kTileBytes, smem_v);
+          mma_commit(smem_u32(&sh.sdp_full));
+        }
+        ok = mbar_wait(smem_u32(&sh.pds_ready), t & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        issue_tt(tDV, smem_p, smem_do + s * Cfg::kTileBytes, t > 0);
+        issue_tt(tDK, smem_ds, smem_q + s * Cfg::kTileBytes, t > 0);
+        if (!Cfg::kAliasDq && t > 0) {
+          ok = mbar_wait(smem_u32(&sh.dq_consumed), (t - 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        issue_dq(tDQ, smem_ds, smem_k);
+        mma_commit(smem_u32(&sh.dq_full));
+        mma_commit(smem_u32(&sh.pds_free));
+        mma_commit(smem_u32(&sh.q_empty[s]));
+        if (Cfg::kQStages == 1 && has_next) {
+          ok = mbar_wait(smem_u32(&sh.q_full[0]), (t + 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_kk(tS, smem_q, smem_k);
+          if (Cfg::kAliasDq) {
+            ok = mbar_wait(smem_u32(&sh.dq_consumed), t & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          issue_kk(tDP, smem_do, smem_v);
+          mma_commit(smem_u32(&sh.sdp_full));
+        }
+      }
+    }
+  } else if (warp < 4) {
+    // ------------------------------------------------------------------ compute group
+    reg_alloc<240>();
+    const int row = tid;  // 0..127
+    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t tS = tmem + Cfg::kTmemS + lane_sel;
+    const uint32_t tDP = tmem + Cfg::kTmemDP + lane_sel;
+    const int64_t bh_sub =
+        (static_cast<int64_t>(b) * ka.drop.heads_total + ka.drop.head_offset + h) * 256;
+    const int L16 = (sq + 15) >> 4;
+    const float* lse_row = ka.lse + (static_cast<int64_t>(b) * ka.heads + h) * ka.lse_stride;
+    const float* d_row = a.softmax_d + (static_cast<int64_t>(b) * ka.heads + h) * ka.lse_stride;
+    bool ok = true;
+
+    for (int t = 0; t < nm && ok; ++t) {
+      const int m0 = (m_begin + t) * kBM;
+      const int ig = m0 + row;
+      const bool row_valid = ig < sq;
+      const float lse2 = row_valid ? lse_row[ig] * 1.4426950408889634f : INFINITY;
+      const float d_i = row_valid ? d_row[ig] : 0.f;
+      bool row_in_layout = true;
+      int32_t bs_it = 0;
+      if constexpr (BLOCKSPARSE) {
+        bs_it = ka.bs_iter[(static_cast<int64_t>(b) * ka.bs_kblocks + (n0 >> 8)) * ka.bs_rows16 +
+                           (ig >> 4)];
+        row_in_layout = bs_it >= 0;
+      }
+
+      ok = mbar_wait(smem_u32(&sh.sdp_full), t & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+
+      uint32_t pp[64], pds[64];
+      const bool need_mask = (n0 + kBN > sk) || (CAUSAL && (n0 + kBN - 1 > m0));
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sr[32], dr[32];
+        tmem_ld32(tS + c * 32, sr);
+        tmem_ld32(tDP + c * 32, dr);
+        tmem_wait_ld();
+        uint32_t keep = 0xffffffffu;
+        if constexpr (DROPOUT) {
+          keep = 0;
+#pragma unroll
+          for (int hg = 0; hg < 2; ++hg) {
+            const int jg0 = n0 + c * 32 + hg * 16;
+            int64_t it;
+            if constexpr (BLOCKSPARSE) it = bs_it;
+            else it = fa_iter_index(CAUSAL, jg0 >> ka.drop.n_shift, ig >> 4, L16, ka.drop.n_shift);
+            keep |= fa_dropout_keep16(ka.drop, bh_sub, ig, jg0, it) << (hg * 16);
+          }
+        }
+        float pv[32], dsv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float p = ex2(fmaf(__uint_as_float(sr[i]), ka.scale_log2, -lse2));
+          if (need_mask) {
+            const int col = n0 + c * 32 + i;
+            bool valid = col < sk;
+            if (CAUSAL) valid = valid && (col <= ig);
+            if (!valid) p = 0.f;
+          }
+          if (BLOCKSPARSE && !row_in_layout) p = 0.f;
+          const float dp = __uint_as_float(dr[i]);
+          const bool kept = (keep >> i) & 1u;
+          pv[i] = kept ? p : 0.f;
+          dsv[i] = kept ? p * (dp - d_i) : -p * d_i;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          pp[c * 16 + i] = pack16<BF16>(pv[2 * i], pv[2 * i + 1]);
+          pds[c * 16 + i] = pack16<BF16>(dsv[2 * i], dsv[2 * i + 1]);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sh.sdp_consumed));
+
+      if (t > 0) {
+        ok = mbar_wait(smem_u32(&sh.pds_free), (t - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      // 128 16-bit values per row = 16 chunks of 16 bytes, two 64-column panels
+#pragma unroll
+      for (int ch = 0; ch < 16; ++ch) {
+        const uint32_t off = (ch >> 3) * 16384 + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
+        *reinterpret_cast<uint4*>(p_ptr + off) =
+            make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
+        *reinterpret_cast<uint4*>(ds_ptr + off) =
+            make_uint4(pds[4 * ch], pds[4 * ch + 1], pds[4 * ch + 2], pds[4 * ch + 3]);
+      }
+      fence_async_smem();
+      mbar_arrive(smem_u32(&sh.pds_ready));
+    }
+
+    // ---------------- epilogue: dV = acc / p_keep
+    if (ok) {
+      ok = mbar_wait(smem_u32(&sh.pds_free), (nm - 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const uint32_t tDV = tmem + Cfg::kTmemDV + lane_sel;
+      const int kr = n0 + row;
+      uint16_t* dst_row = dv_base + static_cast<int64_t>(k_start + kr) * a.dv_row_stride +
+                          static_cast<int64_t>(h) * a.dv_head_stride;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tDV + c * 32, r);
+        tmem_wait_ld();
+        if (kr < sk && c * 32 < ka.head_dim) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            pk[i] = pack16<BF16>(__uint_as_float(r[2 * i]) * rp_keep, __uint_as_float(r[2 * i + 1]) * rp_keep);
+          uint4* dst = reinterpret_cast<uint4*>(dst_row + c * 32);
+          const int nvec = min(4, (ka.head_dim - c * 32) / 8);
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            if (v < nvec) dst[v] = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ dQ group (warps 4-7)
+    reg_dealloc<104>();
+    const int row = tid - 128;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tDQ = tmem + Cfg::kTmemDQ + lane_sel;
+    bool ok = true;
+    for (int t = 0; t < nm && ok; ++t) {
+      const int ig = (m_begin + t) * kBM + row;
+      ok = mbar_wait(smem_u32(&sh.dq_full), t & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      float* acc_row = a.dq_accum + (static_cast<int64_t>(q_start + ig) * ka.heads + h) * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tDQ + c * 32, r);
+        tmem_wait_ld();
+        if (ig < sq) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            red_add_v4(acc_row + c * 32 + i, __uint_as_float(r[i]), __uint_as_float(r[i + 1]),
+                       __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sh.dq_consumed));
+    }
+    // ---------------- epilogue: dK = acc * scale / p_keep
+    if (ok) {
+      tc_fence_after();
+      const uint32_t tDK = tmem + Cfg::kTmemDK + lane_sel;
+      const int kr = n0 + row;
+      const float f = ka.scale * rp_keep;
+      uint16_t* dst_row = dk_base + static_cast<int64_t>(k_start + kr) * a.dk_row_stride +
+                          static_cast<int64_t>(h) * a.dk_head_stride;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tDK + c * 32, r);
+        tmem_wait_ld();
+        if (kr < sk && c * 32 < ka.head_dim) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            pk[i] = pack16<BF16>(__uint_as_float(r[2 * i]) * f, __uint_as_float(r[2 * i + 1]) * f);
+          uint4* dst = reinterpret_cast<uint4*>(dst_row + c * 32);
+          const int nvec = min(4, (ka.head_dim - c * 32) / 8);
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            if (v < nvec) dst[v] = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tmem_dealloc(tmem, 512);
+    if (lane == 0 && sh.abort_flag && ka.status) atomicExch(ka.status + 1, 1);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// softmax_d = p_keep * rowsum(dO * O); zero the dQ accumulator.  One thread per 8 elements.
+template <bool BF16>
+__global__ void bwd_preprocess_kernel(const BwdArgs a, int dpad) {
+  const KernelArgs& ka = a.k;
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int q_start = ka.cu_seqlens_q[b];
+  const int sq = ka.cu_seqlens_q[b + 1] - q_start;
+  const int d = ka.head_dim;
+  const int tpr = d / 8;                      // threads per row: 2, 4, 8 or 16
+  const int rows_per_block = blockDim.x / tpr;
+  const int r = threadIdx.x / tpr, c = (threadIdx.x % tpr) * 8;
+  const int i = blockIdx.x * rows_per_block + r;
+  float acc = 0.f;
+  if (i < sq) {
+    const int64_t row = q_start + i;
+    const uint16_t* o = reinterpret_cast<const uint16_t*>(a.o_in) + row * ka.o_row_stride + h * ka.o_head_stride + c;
+    const uint16_t* g = reinterpret_cast<const uint16_t*>(a.dout) + row * a.do_row_stride + h * a.do_head_stride + c;
+    const uint4 ov = *reinterpret_cast<const uint4*>(o);
+    const uint4 gv = *reinterpret_cast<const uint4*>(g);
+    const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w}, gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 of, gf;
+      if constexpr (BF16) {
+        of = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ow[k]));
+        gf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[k]));
+      } else {
+        of = __half22float2(*reinterpret_cast<const __half2*>(&ow[k]));
+        gf = __half22float2(*reinterpret_cast<const __half2*>(&gw[k]));
+      }
+      acc += of.x * gf.x + of.y * gf.y;
+    }
+    // zero this thread's share of the fp32 dQ accumulator row (dpad floats per (row, head))
+    float* zr = a.dq_accum + (row * ka.heads + h) * dpad;
+    for (int z = (threadIdx.x % tpr) * 4; z < dpad; z += tpr * 4)
+      *reinterpret_cast<float4*>(zr + z) = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int off = tpr / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (i < sq && (threadIdx.x % tpr) == 0)
+    a.softmax_d[(static_cast<int64_t>(b) * ka.heads + h) * ka.lse_stride + i] = acc * a.p_keep;
+}
+
+// dq = accumulator * scale / p_keep.  One thread per 8 elements.
+template <bool BF16>
+__global__ void bwd_postprocess_kernel(const BwdArgs a, int dpad) {
+  const KernelArgs& ka = a.k;
+  const int d = ka.head_dim;
+  const int tpr = d / 8;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t total = static_cast<int64_t>(a.total_q) * ka.heads * tpr;
+  if (idx >= total) return;
+  const int c = static_cast<int>(idx % tpr) * 8;
+  const int64_t rh = idx / tpr;
+  const int h = static_cast<int>(rh % ka.heads);
+  const int64_t row = rh / ka.heads;
+  const float* src = a.dq_accum + rh * dpad + c;
+  const float4 x = *reinterpret_cast<const float4*>(src);
+  const float4 y = *reinterpret_cast<const float4*>(src + 4);
+  const float f = ka.scale * ka.rp_keep;
+  uint4 out;
+  out.x = pack16<BF16>(x.x * f, x.y * f);
+  out.y = pack16<BF16>(x.z * f, x.w * f);
+  out.z = pack16<BF16>(y.x * f, y.y * f);
+  out.w = pack16<BF16>(y.z * f, y.w * f);
+  uint16_t* dst = reinterpret_cast<uint16_t*>(a.dq) + row * a.dq_row_stride + h * a.dq_head_stride + c;
+  *reinterpret_cast<uint4*>(dst) = out;
+}
+
+template <int D, bool BF16, bool CAUSAL, bool DROPOUT, bool BS>
+cudaError_t launch_main(const BwdLaunch& l, cudaStream_t stream) {
+  auto kernel = fa_bwd_kernel<D, BF16, CAUSAL, DROPOUT, BS>;
+  constexpr int smem = BwdCfg<D>::kSmemBytes;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  dim3 grid((l.args.max_seqlen_k + kBN - 1) / kBN, l.args.k.heads, l.args.k.batch);
+  kernel<<<grid, kBwdThreads, smem, stream>>>(l.tm_q, l.tm_k, l.tm_v, l.tm_do, l.args);
+  return cudaGetLastError();
+}
+
+template <int D, bool BF16, bool CAUSAL>
+cudaError_t launch_dd(const BwdLaunch& l, cudaStream_t stream) {
+  const bool bs = l.args.k.bs_iter != nullptr;
+  if (l.is_dropout) {
+    return bs ? launch_main<D, BF16, CAUSAL, true, true>(l, stream)
+              : launch_main<D, BF16, CAUSAL, true, false>(l, stream);
+  }
+  return bs ? launch_main<D, BF16, CAUSAL, false, true>(l, stream)
+            : launch_main<D, BF16, CAUSAL, false, false>(l, stream);
+}
+
+template <int D>
+cudaError_t launch_d(const BwdLaunch& l, cudaStream_t stream) {
+  if (l.is_bf16) {
+    return l.is_causal ? launch_dd<D, true, true>(l, stream) : launch_dd<D, true, false>(l, stream);
+  }
+  return l.is_causal ? launch_dd<D, false, true>(l, stream) : launch_dd<D, false, false>(l, stream);
+}
+
+}  // namespace
+
+cudaError_t launch_bwd(const BwdLaunch& l, cudaStream_t stream) {
+  const BwdArgs& a = l.args;
+  const int d = a.k.head_dim;
+  // 1. preprocess
+  {
+    const int tpr = d / 8;
+    const int threads = 256;
+    const int rows_per_block = threads / tpr;
+    dim3 grid((a.max_seqlen_q + rows_per_block - 1) / rows_per_block, a.k.heads, a.k.batch);
+    if (l.is_bf16) bwd_preprocess_kernel<true><<<grid, threads, 0, stream>>>(a, l.dpad);
+    else bwd_preprocess_kernel<false><<<grid, threads, 0, stream>>>(a, l.dpad);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  // 2. main
+  {
+    cudaError_t e = l.dpad == 64 ? launch_d<64>(l, stream) : launch_d<128>(l, stream);
+    if (e != cudaSuccess) return e;
+  }
+  // 3. postprocess
+  {
+    const int64_t total = static_cast<int64_t>(a.total_q) * a.k.heads * (d / 8);
+    if (total > 0) {
+      const int threads = 256;
+      const int blocks = static_cast<int>((total + threads - 1) / threads);
+      if (l.is_bf16) bwd_postprocess_kernel<true><<<blocks, threads, 0, stream>>>(a, l.dpad);
+      else bwd_postprocess_kernel<false><<<blocks, threads, 0, stream>>>(a, l.dpad);
+      cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return e;
+    }
+  }
+  return cudaSuccess;
+}
+
+}  // namespace fa

@@ -50,7 +50,15 @@ struct FwdLaunch {
   int32_t dpad;  // 64 or 128
 };
 
+struct BwdLaunch {
+  CUtensorMap tm_q, tm_k, tm_v, tm_do;
+  BwdArgs args;
+  bool is_bf16, is_causal, is_dropout;
+  int32_t dpad;  // 64 or 128
+};
+
 cudaError_t launch_fwd(const FwdLaunch& l, cudaStream_t stream);
+cudaError_t launch_bwd(const BwdLaunch& l, cudaStream_t stream);
 cudaError_t launch_dropout_mask(uint8_t* out, int b, int h, const DropoutParams& dp, bool causal,
                                 int sq, int sk, const int32_t* bs_iter, int bs_kblocks,
                                 int bs_rows16, cudaStream_t stream);

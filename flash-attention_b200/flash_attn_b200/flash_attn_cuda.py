@@ -132,3 +132,66 @@ def fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropo
                   p_dropout, softmax_scale, is_causal, seed, offset)
         check(lib.fa_fwd(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return [o, lse]
+
+
+_workspaces = {}
+
+
+def _workspace(device, nbytes):
+    """Scratch for the fp32 dQ accumulator; grown on demand and reused by later calls on the same
+    device (calls on one device are ordered by the stream they run on)."""
+    ws = _workspaces.get(device)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
+        _workspaces[device] = ws
+    return ws
+
+
+def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
+        max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, gen=None):
+    """mha_bwd (csrc/flash_attn/fmha_api.cpp:302-449): writes dq, dk, dv in place and returns
+    [dq, dk, dv, softmax_d]."""
+    batch, total_q, total_k, heads, d = _check_qkv(q, k, v, cu_seqlens_q, cu_seqlens_k)
+    _require(dout.dtype == q.dtype and out.dtype == q.dtype, "dout / out dtype mismatch")
+    _require(dq.dtype == q.dtype and dk.dtype == q.dtype and dv.dtype == q.dtype,
+             "dq / dk / dv dtype mismatch")
+    _require(out.is_contiguous() and dout.is_contiguous(), "out and dout must be contiguous")
+    _require(tuple(out.shape) == (total_q, heads, d) and tuple(dout.shape) == (total_q, heads, d),
+             "out / dout have the wrong shape")
+    _require(tuple(dq.shape) == (total_q, heads, d), "dq has the wrong shape")
+    _require(tuple(dk.shape) == (total_k, heads, d) and tuple(dv.shape) == (total_k, heads, d),
+             "dk / dv have the wrong shape")
+    _require(dq.stride(-1) == 1 and dk.stride(-1) == 1 and dv.stride(-1) == 1,
+             "dq, dk, dv must have a contiguous last dimension")
+    _require(softmax_lse.dtype == torch.float32 and softmax_lse.dim() == 3
+             and softmax_lse.shape[0] == batch and softmax_lse.shape[1] == heads
+             and softmax_lse.shape[2] >= max_seqlen_q and softmax_lse.is_contiguous(),
+             "softmax_lse must be a contiguous fp32 (batch, heads, >= max_seqlen_q) tensor")
+    _require(p_dropout < 1.0, "p_dropout must be < 1")
+    with torch.cuda.device(q.device):
+        if zero_tensors:
+            dq.zero_()
+            dk.zero_()
+            dv.zero_()
+        softmax_d = torch.empty_like(softmax_lse)
+        seed, offset = 0, 0
+        if p_dropout > 0:
+            # The caller restores the generator state saved before the forward, so reading the
+            # state here yields the forward's (seed, offset); the reference then advances it by a
+            # dummy amount (csrc/flash_attn/fmha_api.cpp:437-445).
+            seed, offset = _philox_state(gen, 4)
+        p = BwdParams()
+        _fill_fwd(p.fwd, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
+                  max_seqlen_k, p_dropout, softmax_scale, is_causal, seed, offset)
+        p.dout = dout.data_ptr()
+        p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+        p.softmax_d = softmax_d.data_ptr()
+        p.dq_row_stride, p.dq_head_stride = dq.stride(0), dq.stride(1)
+        p.dk_row_stride, p.dk_head_stride = dk.stride(0), dk.stride(1)
+        p.dv_row_stride, p.dv_head_stride = dv.stride(0), dv.stride(1)
+        nbytes = lib.fa_bwd_workspace_bytes(total_q, heads, d)
+        ws = _workspace(q.device, nbytes)
+        p.workspace = ws.data_ptr()
+        p.workspace_bytes = ws.numel()
+        check(lib.fa_bwd(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return [dq, dk, dv, softmax_d]
