@@ -1,0 +1,417 @@
+"""Benchmark of the attention hot path (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--seqlen S]
+
+Workload (default): BERT-base-shaped varlen training attention -- batch 8, 12 heads, head_dim 64,
+fp16, max_seqlen 4096, per-sequence lengths uniform in [max/2, max] from a seed, packed with
+cu_seqlens, dropout 0.1, non-causal, Q/K/V/dO ~ N(0,1); synthetic data standing in for the
+BERT-base attention shapes of the reference's speed-up chart.  One step = one forward + backward
+pass over that batch.  Metric: algorithmic TFLOP/s, 3.5 * 4 * d * heads * sum(s_i^2) per step.
+
+The printed JSON line follows the driver's contract: `value` is measured with inputs resident in
+HBM, `e2e` through the public functional API with pinned host buffers copied in and results
+copied out inside the timed region, `roofline` for the dominant kernel (backward main kernel)
+against the measured tensor-core peak, `cpu_baseline` = the CPU oracle (standard attention in
+fp32) timed on a bounded sample on this host.  With N > 1 (one process per GPU under torchrun)
+every rank runs its own batch shard (weak scaling, no data-path collective) and the outputs are
+re-assembled with one NCCL all-gather per step.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "flash-attention_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+BATCH, HEADS, HEAD_DIM = 8, 12, 64
+DROPOUT_P = 0.1
+METRIC = "fwd+bwd attention TFLOP/s (algorithmic, 3.5 x forward)"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"tflops": float(d["bf16_tflops"]), "tflops_sustained": float(d["bf16_tflops_sustained"]),
+                "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"tflops": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def workload_lengths(max_seqlen, seed, batch=BATCH):
+    rng = np.random.RandomState(seed)
+    return rng.randint(max_seqlen // 2, max_seqlen + 1, size=batch).tolist()
+
+
+def fwd_flops(lengths, heads=HEADS, d=HEAD_DIM, causal=False):
+    return 4.0 * d * heads * sum(float(s) * float(s) for s in lengths) * (0.5 if causal else 1.0)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(max(smax)) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_attention_sample(seqlen, heads, d, causal, threads, repeats=1):
+    """fwd+bwd of the oracle's standard attention (fp32) for one sequence of `seqlen` tokens;
+    returns (seconds per pass, flops per pass)."""
+    from oracle import attention_oracle as orc
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    qkv = torch.randn(1, seqlen, 3, heads, d, generator=g, requires_grad=True)
+    dout = torch.randn(1, seqlen, heads, d, generator=g)
+    mask = torch.ones(1, seqlen, dtype=torch.bool)
+    best = float("inf")
+    for _ in range(repeats + 1):  # first pass is the warm-up
+        qkv.grad = None
+        t0 = time.perf_counter()
+        out = orc.attention_ref(qkv, mask, 0.0, upcast=True, causal=causal)
+        out.backward(dout)
+        dt = time.perf_counter() - t0
+        best = min(best, dt) if _ > 0 else best
+    return best, 3.5 * fwd_flops([seqlen], heads, d, causal)
+
+
+def run_reference(args):
+    """--impl reference: the reference's CPU implementation of the path (its standard attention,
+    restated in oracle/, since the reference tree is not present on the GPU box and its CUDA
+    kernels target sm75/sm80 only) on all host threads, on a bounded sample of the workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    lengths = workload_lengths(args.seqlen, args.seed)
+    sample_len = min(max(lengths), 2048)
+    times = []
+    flops = 0.0
+    for i in range(args.warmup + args.steps):
+        dt, flops = cpu_attention_sample(sample_len, HEADS, HEAD_DIM, False, threads, repeats=1)
+        if i >= args.warmup:
+            times.append(dt)
+    t = float(np.mean(times))
+    value = flops / t / 1e12
+    sample = "1 sequence of %d tokens x %d heads, dropout off, fp32 standard attention" % (sample_len, HEADS)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, lengths),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, lengths):
+    return {"workload": "BERT-base varlen attention fwd+bwd: batch %d x %d heads x d %d, fp16, "
+                        "max_seqlen %d, lengths U[max/2,max], dropout %.1f, non-causal"
+                        % (BATCH, HEADS, HEAD_DIM, args.seqlen, DROPOUT_P),
+            "batch_per_gpu": BATCH, "heads": HEADS, "head_dim": HEAD_DIM, "max_seqlen": args.seqlen,
+            "total_tokens_per_gpu": int(sum(lengths)), "dropout_p": DROPOUT_P, "causal": False,
+            "parallelism": "batch shards, one per GPU; outputs all-gathered",
+            "l2": "working set (qkv, dout, out, dqkv, fp32 dq accumulator) exceeds the 126 MB L2"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seqlen", type=int, default=4096)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-extras", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch.distributed as dist
+    from flash_attn_b200 import flash_attn_cuda as fc
+    from flash_attn_b200 import parallel
+    from flash_attn_b200.bert_padding import unpad_input
+    from flash_attn_b200.flash_attn_interface import flash_attn_unpadded_qkvpacked_func
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ------------------------------------------------------------------ synthetic workload
+    lengths = workload_lengths(args.seqlen, args.seed)          # same lengths on every rank
+    S = args.seqlen
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)    # different data per rank
+    padded = torch.randn(BATCH, S, 3 * HEADS * HEAD_DIM, device=dev, dtype=torch.float16, generator=g)
+    mask = torch.arange(S, device=dev)[None, :] < torch.tensor(lengths, device=dev)[:, None]
+    x_unpad, _, cu, max_s = unpad_input(padded, mask)
+    del padded
+    qkv = x_unpad.reshape(-1, 3, HEADS, HEAD_DIM).contiguous()
+    total = qkv.shape[0]
+    dout = torch.randn(total, HEADS, HEAD_DIM, device=dev, dtype=torch.float16, generator=g)
+    scale = HEAD_DIM ** -0.5
+    q, k, v = qkv[:, 0], qkv[:, 1], qkv[:, 2]
+    dqkv = torch.empty_like(qkv)
+    gen = torch.cuda.default_generators[local_rank]
+    torch.cuda.manual_seed(1234)
+    side = torch.cuda.Stream(device=dev)
+
+    def step_resident():
+        """forward + backward through the extension-module contract (C ABI), data in HBM."""
+        state = gen.get_state()
+        out, lse = fc.fwd(q, k, v, cu, cu, max_s, max_s, DROPOUT_P, scale, False, False, False, None)
+        finish = None
+        if world > 1:
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                gathered, work = parallel.all_gather_tokens(out, async_op=True)
+            finish = (gathered, work)
+        after = gen.get_state()
+        gen.set_state(state)  # the backward regenerates the forward's mask
+        fc.bwd(dout, q, k, v, out, lse, dqkv[:, 0], dqkv[:, 1], dqkv[:, 2], cu, cu, max_s, max_s,
+               DROPOUT_P, scale, False, False, None)
+        gen.set_state(after)
+        if finish is not None:
+            finish[1].wait()
+            torch.cuda.current_stream().wait_stream(side)
+        return out
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = t.item()
+        return ms
+
+    flops_fwd = fwd_flops(lengths)
+    flops_step = 3.5 * flops_fwd
+    peaks = measured_peaks()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.3)  # let the first samples arrive before the timed region starts
+    ms_step = timed(step_resident, args.steps, args.warmup)
+    fc.check_device_status(dev)
+    value = world * flops_step / (ms_step * 1e-3) / 1e12
+
+    # ------------------------------------------------------------------ end to end (host buffers)
+    qkv_host = qkv.cpu().pin_memory()
+    dout_host = dout.cpu().pin_memory()
+    out_host = torch.empty((total, HEADS, HEAD_DIM), dtype=torch.float16).pin_memory()
+    dqkv_host = torch.empty_like(qkv_host).pin_memory()
+    qkv_dev = torch.empty_like(qkv)
+    dout_dev = torch.empty_like(dout)
+
+    def step_e2e():
+        qkv_dev.copy_(qkv_host, non_blocking=True)
+        dout_dev.copy_(dout_host, non_blocking=True)
+        x = qkv_dev.detach().requires_grad_()
+        out = flash_attn_unpadded_qkvpacked_func(x, cu, max_s, DROPOUT_P, softmax_scale=scale, causal=False)
+        out.backward(dout_dev)
+        out_host.copy_(out.detach(), non_blocking=True)
+        dqkv_host.copy_(x.grad, non_blocking=True)
+
+    ms_e2e = timed(step_e2e, max(3, args.steps // 2), 3)
+    e2e_value = world * flops_step / (ms_e2e * 1e-3) / 1e12
+    h2d = qkv_host.numel() * 2 + dout_host.numel() * 2
+    d2h = out_host.numel() * 2 + dqkv_host.numel() * 2
+
+    # ------------------------------------------------------------------ kernel-level numbers
+    out, lse = fc.fwd(q, k, v, cu, cu, max_s, max_s, DROPOUT_P, scale, False, False, False, None)
+
+    def fwd_only():
+        fc.fwd(q, k, v, cu, cu, max_s, max_s, DROPOUT_P, scale, False, False, False, None)
+
+    def bwd_main_only():
+        fc.bwd(dout, q, k, v, out, lse, dqkv[:, 0], dqkv[:, 1], dqkv[:, 2], cu, cu, max_s, max_s,
+               DROPOUT_P, scale, False, False, None, _stage_mask=2)
+
+    def bwd_all():
+        fc.bwd(dout, q, k, v, out, lse, dqkv[:, 0], dqkv[:, 1], dqkv[:, 2], cu, cu, max_s, max_s,
+               DROPOUT_P, scale, False, False, None)
+
+    ms_fwd = timed(fwd_only, args.steps, 3)
+    ms_bwd = timed(bwd_all, args.steps, 3)
+    ms_bwd_main = timed(bwd_main_only, args.steps, 3)
+    clocks = sampler.stop()
+    achieved = 2.5 * flops_fwd / (ms_bwd_main * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "fa_bwd_kernel (backward main kernel)",
+                "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                "frac": achieved / peaks["tflops"], "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
+                "traffic": None,
+                "fwd_kernel": {"achieved": flops_fwd / (ms_fwd * 1e-3) / 1e12,
+                               "frac": flops_fwd / (ms_fwd * 1e-3) / 1e12 / peaks["tflops"]}}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
+        "config": workload_config(args, lengths),
+        "pct_of_peak": 100.0 * value / world / peaks["tflops"],
+        "fwd_tflops_per_gpu": flops_fwd / (ms_fwd * 1e-3) / 1e12,
+        "bwd_tflops_per_gpu": 2.5 * flops_fwd / (ms_bwd * 1e-3) / 1e12,
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": 4 * args.steps,
+        "roofline": roofline,
+    }
+
+    if rank == 0 and world == 1:
+        threads = os.cpu_count() or 1
+        sample_len = min(max(lengths), 2048)
+        dt, fl = cpu_attention_sample(sample_len, HEADS, HEAD_DIM, False, threads, repeats=2)
+        line["cpu_baseline"] = {
+            "value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": "1 sequence of %d tokens x %d heads, fp32 standard attention fwd+bwd, dropout off"
+                      % (sample_len, HEADS)}
+        if not args.no_extras:
+            line["extras"] = extras(fc, dev, peaks)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def extras(fc, dev, peaks):
+    """Short sweeps over the other benchmark configurations (few iterations each, kernel time
+    only, data resident): reported for context, not part of the headline value."""
+    res = {}
+
+    def time_fwd_bwd(q, k, v, dout, cu, S, p, causal, scale, iters=5):
+        out, lse = fc.fwd(q, k, v, cu, cu, S, S, p, scale, False, causal, False, None)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        for _ in range(2):
+            fc.fwd(q, k, v, cu, cu, S, S, p, scale, False, causal, False, None)
+            fc.bwd(dout, q, k, v, out, lse, dq, dk, dv, cu, cu, S, S, p, scale, False, causal, None)
+        torch.cuda.synchronize()
+        ev[0].record()
+        for _ in range(iters):
+            fc.fwd(q, k, v, cu, cu, S, S, p, scale, False, causal, False, None)
+        ev[1].record()
+        for _ in range(iters):
+            fc.bwd(dout, q, k, v, out, lse, dq, dk, dv, cu, cu, S, S, p, scale, False, causal, None)
+        ev[2].record()
+        torch.cuda.synchronize()
+        return ev[0].elapsed_time(ev[1]) / iters, ev[1].elapsed_time(ev[2]) / iters
+
+    g = torch.Generator(device=dev).manual_seed(5)
+    # BERT-base varlen sweep (fp16, dropout 0.1)
+    for S in (128, 256, 512, 1024, 2048, 4096):
+        lengths = workload_lengths(S, 0)
+        total = sum(lengths)
+        cu = torch.tensor(np.concatenate([[0], np.cumsum(lengths)]), dtype=torch.int32, device=dev)
+        qkv = torch.randn(total, 3, HEADS, HEAD_DIM, device=dev, dtype=torch.float16, generator=g)
+        dout = torch.randn(total, HEADS, HEAD_DIM, device=dev, dtype=torch.float16, generator=g)
+        f, b = time_fwd_bwd(qkv[:, 0], qkv[:, 1], qkv[:, 2], dout, cu, S, DROPOUT_P, False, 0.125)
+        fl = fwd_flops(lengths)
+        entry = {"fwd_ms": f, "bwd_ms": b, "fwd_tflops": fl / f / 1e9, "fwd_bwd_tflops": 3.5 * fl / (f + b) / 1e9,
+                 "fwd_bwd_pct_peak": 100 * 3.5 * fl / (f + b) / 1e9 / peaks["tflops"]}
+        if S <= 512:
+            hd = HEADS * HEAD_DIM
+            fwd_bytes = 2 * 3 * total * hd + 2 * total * hd + 4 * BATCH * HEADS * S
+            bwd_bytes = 2 * hd * 5 * total + 2 * hd * 3 * total + 8 * BATCH * HEADS * S
+            entry["fwd_gbs"] = fwd_bytes / f / 1e6
+            entry["bwd_gbs"] = bwd_bytes / b / 1e6
+            entry["fwd_pct_hbm_peak"] = 100 * fwd_bytes / f / 1e6 / peaks["hbm_gbs"]
+        res["bert_varlen_fp16_dropout_S%d" % S] = entry
+    # causal LM (bf16, d = 128)
+    for S in (512, 1024, 2048, 4096, 8192):
+        B, H, d = 16, 12, 128
+        cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=dev)
+        q = torch.randn(B * S, H, d, device=dev, dtype=torch.bfloat16, generator=g)
+        k = torch.randn(B * S, H, d, device=dev, dtype=torch.bfloat16, generator=g)
+        v = torch.randn(B * S, H, d, device=dev, dtype=torch.bfloat16, generator=g)
+        dout = torch.randn(B * S, H, d, device=dev, dtype=torch.bfloat16, generator=g)
+        f, b = time_fwd_bwd(q, k, v, dout, cu, S, 0.0, True, d ** -0.5, iters=3)
+        fl = fwd_flops([S] * B, H, d, causal=True)
+        res["causal_lm_bf16_d128_S%d" % S] = {
+            "fwd_ms": f, "bwd_ms": b, "fwd_tflops": fl / f / 1e9, "fwd_bwd_tflops": 3.5 * fl / (f + b) / 1e9,
+            "fwd_pct_peak": 100 * fl / f / 1e9 / peaks["tflops"],
+            "fwd_bwd_pct_peak": 100 * 3.5 * fl / (f + b) / 1e9 / peaks["tflops"]}
+        del q, k, v, dout
+    return res
+
+
+if __name__ == "__main__":
+    main()

@@ -251,6 +251,7 @@ int fa_bwd(const fa_bwd_params* p, void* cuda_stream) {
   l.is_bf16 = f->is_bf16 != 0;
   l.is_causal = f->is_causal != 0;
   l.is_dropout = f->p_dropout > 0.f;
+  l.stage_mask = p->stage_mask;
   fa::BwdArgs& a = l.args;
   a.o_in = f->o;
   a.dout = p->dout;

@@ -576,8 +576,9 @@ cudaError_t launch_d(const BwdLaunch& l, cudaStream_t stream) {
 cudaError_t launch_bwd(const BwdLaunch& l, cudaStream_t stream) {
   const BwdArgs& a = l.args;
   const int d = a.k.head_dim;
+  const int stages = l.stage_mask == 0 ? 7 : l.stage_mask;
   // 1. preprocess
-  {
+  if (stages & 1) {
     const int tpr = d / 8;
     const int threads = 256;
     const int rows_per_block = threads / tpr;
@@ -588,12 +589,12 @@ cudaError_t launch_bwd(const BwdLaunch& l, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
   }
   // 2. main
-  {
+  if (stages & 2) {
     cudaError_t e = l.dpad == 64 ? launch_d<64>(l, stream) : launch_d<128>(l, stream);
     if (e != cudaSuccess) return e;
   }
   // 3. postprocess
-  {
+  if (stages & 4) {
     const int64_t total = static_cast<int64_t>(a.total_q) * a.k.heads * (d / 8);
     if (total > 0) {
       const int threads = 256;

@@ -55,6 +55,7 @@ struct BwdLaunch {
   BwdArgs args;
   bool is_bf16, is_causal, is_dropout;
   int32_t dpad;  // 64 or 128
+  int32_t stage_mask;  // 0 = all; 1 preprocess, 2 main, 4 postprocess
 };
 
 cudaError_t launch_fwd(const FwdLaunch& l, cudaStream_t stream);

@@ -87,6 +87,7 @@ class BwdParams(ctypes.Structure):
         ("dv_head_stride", ctypes.c_int64),
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_size_t),
+        ("stage_mask", ctypes.c_int32),
     ]
 
 

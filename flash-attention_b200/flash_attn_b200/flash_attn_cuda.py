@@ -148,7 +148,7 @@ def _workspace(device, nbytes):
 
 
 def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
-        max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, gen=None):
+        max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, gen=None, _stage_mask=0):
     """mha_bwd (csrc/flash_attn/fmha_api.cpp:302-449): writes dq, dk, dv in place and returns
     [dq, dk, dv, softmax_d]."""
     batch, total_q, total_k, heads, d = _check_qkv(q, k, v, cu_seqlens_q, cu_seqlens_k)
@@ -193,5 +193,6 @@ def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
         ws = _workspace(q.device, nbytes)
         p.workspace = ws.data_ptr()
         p.workspace_bytes = ws.numel()
+        p.stage_mask = _stage_mask
         check(lib.fa_bwd(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return [dq, dk, dv, softmax_d]

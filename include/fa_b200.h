@@ -89,6 +89,9 @@ typedef struct fa_bwd_params {
    * ignored; the call clears what it needs. */
   void* workspace;
   size_t workspace_bytes;
+  /* Profiling aid: which of the three backward launches to run.  0 = all; otherwise a bit mask,
+   * 1 = preprocess (softmax_d, accumulator clear), 2 = main kernel, 4 = postprocess (dq write). */
+  int32_t stage_mask;
 } fa_bwd_params;
 
 /* mha_fwd (csrc/flash_attn/fmha_api.cpp:173-299) and, with blockmask != NULL, mha_fwd_block
