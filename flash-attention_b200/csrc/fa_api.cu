@@ -112,6 +112,25 @@ void fill_dropout(const fa_fwd_params* p, fa::KernelArgs* a) {
   a->drop.head_offset = p->mask_heads_total > 0 ? p->mask_head_offset : 0;
 }
 
+// Block-sparse: check the scratch, build the block-visit table on the stream, point the kernel
+// arguments at it.
+int setup_blocksparse(const fa_fwd_params* p, fa::KernelArgs* a, cudaStream_t stream) {
+  const int nk = p->blockmask_rows;
+  const int nr = p->blockmask_cols;
+  FA_REQUIRE(nk >= round_up(p->max_seqlen_k, 256) / 256, "blockmask has too few key-block rows");
+  FA_REQUIRE(nr >= round_up(p->max_seqlen_q, 16) / 16, "blockmask rows are too short for max_seqlen_q");
+  const size_t need = fa_blocksparse_workspace_bytes(p->batch, nk, nr);
+  if (p->bs_workspace == nullptr || p->bs_workspace_bytes < need)
+    return fail(FA_ERR_WORKSPACE, "bs_workspace must hold " + std::to_string(need) + " bytes");
+  FA_REQUIRE(nk <= 4096, "block-sparse attention supports at most 4096 key blocks");
+  int32_t* table = static_cast<int32_t*>(p->bs_workspace);
+  FA_CUDA(fa::launch_bs_table(table, p->blockmask, p->cu_seqlens_q, p->cu_seqlens_k, p->batch, nk, nr, stream));
+  a->bs_iter = table;
+  a->bs_kblocks = nk;
+  a->bs_rows16 = nr;
+  return FA_OK;
+}
+
 void fill_args(const fa_fwd_params* p, fa::KernelArgs* a) {
   std::memset(a, 0, sizeof(*a));
   a->cu_seqlens_q = p->cu_seqlens_q;
@@ -185,12 +204,13 @@ int fa_fwd(const fa_fwd_params* p, void* cuda_stream) {
   FA_REQUIRE((reinterpret_cast<uintptr_t>(p->o) & 15) == 0, "o must be 16-byte aligned");
   FA_REQUIRE(p->o_row_stride % 8 == 0 && p->o_head_stride % 8 == 0,
              "o strides must be multiples of 8 elements");
-  if (p->blockmask) return fail(FA_ERR_UNSUPPORTED, "block-sparse forward is not built yet");
   if (p->s_dmask) return fail(FA_ERR_UNSUPPORTED, "return_softmax is not built yet");
 
   fa::FwdLaunch l;
   std::memset(&l, 0, sizeof(l));
   fill_args(p, &l.args);
+  if (p->blockmask)
+    if (int rc = setup_blocksparse(p, &l.args, static_cast<cudaStream_t>(cuda_stream))) return rc;
   l.dpad = p->head_dim <= 64 ? 64 : 128;
   l.is_bf16 = p->is_bf16 != 0;
   l.is_causal = p->is_causal != 0;
@@ -211,13 +231,20 @@ int fa_debug_dropout_mask(uint8_t* mask_out, int32_t batch_idx, int32_t head_idx
                           const fa_fwd_params* p, int32_t seqlen_q, int32_t seqlen_k,
                           void* cuda_stream) {
   FA_REQUIRE(p != nullptr && mask_out != nullptr, "null argument");
-  FA_REQUIRE(p->blockmask == nullptr, "block-sparse mask dump is not built yet");
   fa::KernelArgs a;
   std::memset(&a, 0, sizeof(a));
   fill_dropout(p, &a);
+  if (p->blockmask)
+    if (int rc = setup_blocksparse(p, &a, static_cast<cudaStream_t>(cuda_stream))) return rc;
   FA_CUDA(fa::launch_dropout_mask(mask_out, batch_idx, head_idx, a.drop, p->is_causal != 0, seqlen_q,
-                                  seqlen_k, nullptr, 0, 0, static_cast<cudaStream_t>(cuda_stream)));
+                                  seqlen_k, a.bs_iter, a.bs_kblocks, a.bs_rows16,
+                                  static_cast<cudaStream_t>(cuda_stream)));
   return FA_OK;
+}
+
+size_t fa_blocksparse_workspace_bytes(int32_t batch, int32_t blockmask_rows, int32_t blockmask_cols) {
+  return static_cast<size_t>(batch) * static_cast<size_t>(blockmask_rows) *
+         static_cast<size_t>(blockmask_cols) * sizeof(int32_t);
 }
 
 size_t fa_bwd_workspace_bytes(int32_t total_q, int32_t heads, int32_t head_dim) {
@@ -238,7 +265,6 @@ int fa_bwd(const fa_bwd_params* p, void* cuda_stream) {
                  p->dk_head_stride % 8 == 0 && p->dv_row_stride % 8 == 0 && p->dv_head_stride % 8 == 0 &&
                  f->o_row_stride % 8 == 0 && f->o_head_stride % 8 == 0,
              "gradient strides must be multiples of 8 elements");
-  if (f->blockmask) return fail(FA_ERR_UNSUPPORTED, "block-sparse backward is not built yet");
   const size_t need = fa_bwd_workspace_bytes(f->total_q, f->heads, f->head_dim);
   if (p->workspace == nullptr || p->workspace_bytes < need)
     return fail(FA_ERR_WORKSPACE, "workspace must hold " + std::to_string(need) + " bytes");
@@ -247,6 +273,8 @@ int fa_bwd(const fa_bwd_params* p, void* cuda_stream) {
   fa::BwdLaunch l;
   std::memset(&l, 0, sizeof(l));
   fill_args(f, &l.args.k);
+  if (f->blockmask)
+    if (int rc = setup_blocksparse(f, &l.args.k, static_cast<cudaStream_t>(cuda_stream))) return rc;
   l.dpad = f->head_dim <= 64 ? 64 : 128;
   l.is_bf16 = f->is_bf16 != 0;
   l.is_causal = f->is_causal != 0;

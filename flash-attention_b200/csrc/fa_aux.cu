@@ -26,7 +26,56 @@ __global__ void dropout_mask_kernel(uint8_t* out, int b, int h, DropoutParams dp
     out[static_cast<int64_t>(i) * sk + jg0 + o] = (keep >> o) & 1u;
 }
 
+// Block-sparse iteration table.  The converted block mask lists, for each 256-column key block,
+// the 16-row query blocks to visit in ascending order (value = 4 * row_block + flags, -1 ends the
+// list).  The reference walks key blocks in order and, inside one, the list until it ends or
+// reaches a row block at or beyond the sequence's query length
+// (csrc/flash_attn/src/fmha_block_fprop_kernel_1xN.h:90-100, :209, :486); key blocks at or beyond
+// the key length are not visited at all (:88).  table[b][kb][rb] = number of blocks visited
+// before (kb, rb), or -1 when (kb, rb) is not visited.  One CTA per batch entry.
+__global__ void bs_table_kernel(int32_t* table, const int32_t* blockmask, const int32_t* cu_q,
+                                const int32_t* cu_k, int nk, int nr) {
+  extern __shared__ int32_t cnt[];  // nk + 1 entries
+  const int b = blockIdx.x;
+  const int sq = cu_q[b + 1] - cu_q[b];
+  const int sk = cu_k[b + 1] - cu_k[b];
+  int32_t* tb = table + static_cast<int64_t>(b) * nk * nr;
+  for (int i = threadIdx.x; i < nk * nr; i += blockDim.x) tb[i] = -1;
+  for (int kb = threadIdx.x; kb < nk; kb += blockDim.x) {
+    int c = 0;
+    if (kb * 256 < sk) {
+      const int32_t* row = blockmask + static_cast<int64_t>(kb) * nr;
+      while (c < nr) {
+        const int32_t v = row[c];
+        if (v < 0 || (v >> 2) * 16 >= sq) break;
+        ++c;
+      }
+    }
+    cnt[kb + 1] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    cnt[0] = 0;
+    for (int kb = 0; kb < nk; ++kb) cnt[kb + 1] += cnt[kb];
+  }
+  __syncthreads();
+  for (int kb = threadIdx.x; kb < nk; kb += blockDim.x) {
+    const int32_t* row = blockmask + static_cast<int64_t>(kb) * nr;
+    const int n = cnt[kb + 1] - cnt[kb];
+    for (int c = 0; c < n; ++c) {
+      const int rb = row[c] >> 2;
+      if (rb >= 0 && rb < nr) tb[static_cast<int64_t>(kb) * nr + rb] = cnt[kb] + c;
+    }
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_bs_table(int32_t* table, const int32_t* blockmask, const int32_t* cu_q,
+                            const int32_t* cu_k, int batch, int nk, int nr, cudaStream_t stream) {
+  bs_table_kernel<<<batch, 256, (nk + 1) * sizeof(int32_t), stream>>>(table, blockmask, cu_q, cu_k, nk, nr);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_dropout_mask(uint8_t* out, int b, int h, const DropoutParams& dp, bool causal,
                                 int sq, int sk, const int32_t* bs_iter, int bs_kblocks,

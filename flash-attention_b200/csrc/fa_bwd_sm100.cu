@@ -33,6 +33,7 @@ namespace {
 constexpr int kBM = 128;  // query rows per tile
 constexpr int kBN = 128;  // key rows per tile
 constexpr int kBwdThreads = 384;
+constexpr int kMaxSparseTiles = 1024;  // query tiles of 128 per sequence in block-sparse mode
 
 template <int D>
 struct BwdCfg {
@@ -113,7 +114,35 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
   const int m_tiles = (sq + kBM - 1) / kBM;
   const int m_begin = CAUSAL ? min(m_tiles, n0 / kBM) : 0;
-  const int nm = m_tiles - m_begin;
+  int nm = m_tiles - m_begin;
+  // block-sparse: query tiles that have at least one 16-row block in this key block's list
+  __shared__ uint16_t qtile_list[BLOCKSPARSE ? kMaxSparseTiles : 1];
+  __shared__ int qtile_count;
+  if constexpr (BLOCKSPARSE) {
+    uint8_t* flags = reinterpret_cast<uint8_t*>(smem_raw);
+    const int32_t* brow = ka.bs_iter + (static_cast<int64_t>(b) * ka.bs_kblocks + (n0 >> 8)) * ka.bs_rows16;
+    const int rb_end = min(ka.bs_rows16, (sq + 15) >> 4);
+    const int mt = min(m_tiles, kMaxSparseTiles);
+    for (int m = threadIdx.x; m < mt; m += kBwdThreads) {
+      bool any = false;
+      for (int rb = m * (kBM / 16); rb < min((m + 1) * (kBM / 16), rb_end); ++rb) any = any || (brow[rb] >= 0);
+      flags[m] = any ? 1 : 0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int n = 0;
+      for (int m = 0; m < mt; ++m)
+        if (flags[m]) qtile_list[n++] = static_cast<uint16_t>(m);
+      qtile_count = n;
+    }
+    __syncthreads();
+    nm = qtile_count;
+    __syncthreads();
+  }
+  auto q_tile = [&](int t) -> int {
+    if constexpr (BLOCKSPARSE) return qtile_list[t];
+    else return m_begin + t;
+  };
 
   uint16_t* dk_base = reinterpret_cast<uint16_t*>(a.dk);
   uint16_t* dv_base = reinterpret_cast<uint16_t*>(a.dv);
@@ -192,7 +221,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (!ok) break;
         const uint32_t bar = smem_u32(&sh.q_full[s]);
         mbar_expect_tx(bar, 2 * Cfg::kTileBytes);
-        const int row = q_start + (m_begin + t) * kBM;
+        const int row = q_start + q_tile(t) * kBM;
         for (int p = 0; p < D / 64; ++p) {
           tma_load_3d(smem_q + s * Cfg::kTileBytes + p * 16384, &tm_q, bar, p * 64, row, h);
           tma_load_3d(smem_do + s * Cfg::kTileBytes + p * 16384, &tm_do, bar, p * 64, row, h);
@@ -297,7 +326,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     bool ok = true;
 
     for (int t = 0; t < nm && ok; ++t) {
-      const int m0 = (m_begin + t) * kBM;
+      const int m0 = q_tile(t) * kBM;
       const int ig = m0 + row;
       const bool row_valid = ig < sq;
       const float lse2 = row_valid ? lse_row[ig] * 1.4426950408889634f : INFINITY;
@@ -305,8 +334,9 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       bool row_in_layout = true;
       int32_t bs_it = 0;
       if constexpr (BLOCKSPARSE) {
-        bs_it = ka.bs_iter[(static_cast<int64_t>(b) * ka.bs_kblocks + (n0 >> 8)) * ka.bs_rows16 +
-                           (ig >> 4)];
+        bs_it = (ig >> 4) < ka.bs_rows16
+                    ? ka.bs_iter[(static_cast<int64_t>(b) * ka.bs_kblocks + (n0 >> 8)) * ka.bs_rows16 + (ig >> 4)]
+                    : -1;
         row_in_layout = bs_it >= 0;
       }
 
@@ -415,7 +445,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const uint32_t tDQ = tmem + Cfg::kTmemDQ + lane_sel;
     bool ok = true;
     for (int t = 0; t < nm && ok; ++t) {
-      const int ig = (m_begin + t) * kBM + row;
+      const int ig = q_tile(t) * kBM + row;
       ok = mbar_wait(smem_u32(&sh.dq_full), t & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -554,13 +584,8 @@ cudaError_t launch_main(const BwdLaunch& l, cudaStream_t stream) {
 
 template <int D, bool BF16, bool CAUSAL>
 cudaError_t launch_dd(const BwdLaunch& l, cudaStream_t stream) {
-  const bool bs = l.args.k.bs_iter != nullptr;
-  if (l.is_dropout) {
-    return bs ? launch_main<D, BF16, CAUSAL, true, true>(l, stream)
-              : launch_main<D, BF16, CAUSAL, true, false>(l, stream);
-  }
-  return bs ? launch_main<D, BF16, CAUSAL, false, true>(l, stream)
-            : launch_main<D, BF16, CAUSAL, false, false>(l, stream);
+  return l.is_dropout ? launch_main<D, BF16, CAUSAL, true, false>(l, stream)
+                      : launch_main<D, BF16, CAUSAL, false, false>(l, stream);
 }
 
 template <int D>
@@ -590,7 +615,14 @@ cudaError_t launch_bwd(const BwdLaunch& l, cudaStream_t stream) {
   }
   // 2. main
   if (stages & 2) {
-    cudaError_t e = l.dpad == 64 ? launch_d<64>(l, stream) : launch_d<128>(l, stream);
+    cudaError_t e;
+    if (a.k.bs_iter != nullptr) {
+      // block-sparse exists for fp16, head_dim <= 64, non-causal only (checked by the C ABI)
+      e = l.is_dropout ? launch_main<64, false, false, true, true>(l, stream)
+                       : launch_main<64, false, false, false, true>(l, stream);
+    } else {
+      e = l.dpad == 64 ? launch_d<64>(l, stream) : launch_d<128>(l, stream);
+    }
     if (e != cudaSuccess) return e;
   }
   // 3. postprocess

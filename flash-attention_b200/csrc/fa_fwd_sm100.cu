@@ -36,6 +36,8 @@ struct FwdCfg {
   static constexpr uint32_t kTmemS0 = 0, kTmemS1 = 128, kTmemO0 = 256, kTmemO1 = 256 + D;
 };
 
+constexpr int kMaxSparseTiles = 1024;  // key tiles of 128 per sequence in block-sparse mode
+
 struct FwdShared {
   uint64_t q_full[2];
   uint64_t k_full[3], k_empty[3], v_full[3], v_empty[3];
@@ -68,6 +70,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   using Cfg = FwdCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ FwdShared sh;
+  // block-sparse: key tiles this CTA visits (ascending), built from the layout table
+  __shared__ uint16_t tile_list[BLOCKSPARSE ? kMaxSparseTiles : 1];
+  __shared__ int tile_count;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -82,7 +87,35 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const int sk = a.cu_seqlens_k[b + 1] - k_start;
   if (mp * 2 * kBlockM >= sq) return;
 
-  const int n_kv_total = (sk + kBlockN - 1) / kBlockN;
+  int n_kv_total = (sk + kBlockN - 1) / kBlockN;
+  if constexpr (BLOCKSPARSE) {
+    // A key tile is visited when any 16-row block of this CTA's 256 query rows has its 256-column
+    // key block in the layout; rows whose block is absent are masked inside the tile.
+    uint8_t* flags = reinterpret_cast<uint8_t*>(smem_raw);
+    const int rb0 = mp * (2 * kBlockM / 16);
+    const int rb1 = min(min(rb0 + 2 * kBlockM / 16, a.bs_rows16), (sq + 15) >> 4);
+    n_kv_total = min(n_kv_total, kMaxSparseTiles);
+    for (int j = tid; j < n_kv_total; j += kFwdThreads) {
+      const int32_t* row = a.bs_iter + (static_cast<int64_t>(b) * a.bs_kblocks + (j >> 1)) * a.bs_rows16;
+      bool any = false;
+      for (int rb = rb0; rb < rb1; ++rb) any = any || (row[rb] >= 0);
+      flags[j] = any ? 1 : 0;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int n = 0;
+      for (int j = 0; j < n_kv_total; ++j)
+        if (flags[j]) tile_list[n++] = static_cast<uint16_t>(j);
+      tile_count = n;
+    }
+    __syncthreads();
+    n_kv_total = tile_count;
+    __syncthreads();  // flags live in the tile buffers: finish reading before TMA may overwrite
+  }
+  auto kv_tile = [&](int j) -> int {
+    if constexpr (BLOCKSPARSE) return tile_list[j];
+    else return j;
+  };
   int m0[2], n_tiles[2];
 #pragma unroll
   for (int g = 0; g < 2; ++g) {
@@ -149,7 +182,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           mbar_expect_tx(bar, Cfg::kTileBytes);
           for (int p = 0; p < Cfg::kPanels; ++p)
             tma_load_3d(smem_k + s * Cfg::kTileBytes + p * 16384, &tm_k, bar, p * 64,
-                        k_start + j * kBlockN, h);
+                        k_start + kv_tile(j) * kBlockN, h);
         }
         if (j >= Cfg::kStages) ok = mbar_wait(smem_u32(&sh.v_empty[s]), ph, abort_flag);
         if (!ok) break;
@@ -158,7 +191,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           mbar_expect_tx(bar, Cfg::kTileBytes);
           for (int p = 0; p < Cfg::kPanels; ++p)
             tma_load_3d(smem_v + s * Cfg::kTileBytes + p * 16384, &tm_v, bar, p * 64,
-                        k_start + j * kBlockN, h);
+                        k_start + kv_tile(j) * kBlockN, h);
         }
       }
     }
@@ -252,7 +285,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sr[c]);
       tmem_wait_ld();
 
-      const int col0 = j * kBlockN;
+      const int col0 = kv_tile(j) * kBlockN;
       bool need_mask = (col0 + kBlockN > sk);
       if (CAUSAL) need_mask = need_mask || (col0 + kBlockN - 1 > m0[g]);
       if (need_mask) {
@@ -269,8 +302,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if constexpr (BLOCKSPARSE) {
         // a 16-row block that is not in the layout for this 256-column key block sees -inf
         const int kb = col0 >> 8;
-        const int32_t it = a.bs_iter[(static_cast<int64_t>(b) * a.bs_kblocks + kb) * a.bs_rows16 +
-                                     (ig >> 4)];
+        const int32_t it = (ig >> 4) < a.bs_rows16
+                               ? a.bs_iter[(static_cast<int64_t>(b) * a.bs_kblocks + kb) * a.bs_rows16 + (ig >> 4)]
+                               : -1;
         if (it < 0) {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
@@ -328,8 +362,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           for (int hgrp = 0; hgrp < 2; ++hgrp) {
             const int jg0 = col0 + c * 32 + hgrp * 16;
             if constexpr (BLOCKSPARSE) {
-              it_index = a.bs_iter[(static_cast<int64_t>(b) * a.bs_kblocks + (jg0 >> 8)) *
-                                       a.bs_rows16 + (ig >> 4)];
+              it_index = (ig >> 4) < a.bs_rows16
+                             ? a.bs_iter[(static_cast<int64_t>(b) * a.bs_kblocks + (jg0 >> 8)) * a.bs_rows16 + (ig >> 4)]
+                             : 0;
             } else {
               it_index = fa_iter_index(CAUSAL, jg0 >> a.drop.n_shift, ig >> 4, L16, a.drop.n_shift);
             }
@@ -419,13 +454,8 @@ cudaError_t launch_one(const FwdLaunch& l, cudaStream_t stream) {
 
 template <int D, bool BF16, bool CAUSAL>
 cudaError_t launch_dd(const FwdLaunch& l, cudaStream_t stream) {
-  const bool bs = l.args.bs_iter != nullptr;
-  if (l.is_dropout) {
-    return bs ? launch_one<D, BF16, CAUSAL, true, true>(l, stream)
-              : launch_one<D, BF16, CAUSAL, true, false>(l, stream);
-  }
-  return bs ? launch_one<D, BF16, CAUSAL, false, true>(l, stream)
-            : launch_one<D, BF16, CAUSAL, false, false>(l, stream);
+  return l.is_dropout ? launch_one<D, BF16, CAUSAL, true, false>(l, stream)
+                      : launch_one<D, BF16, CAUSAL, false, false>(l, stream);
 }
 
 template <int D>
@@ -439,6 +469,11 @@ cudaError_t launch_d(const FwdLaunch& l, cudaStream_t stream) {
 }  // namespace
 
 cudaError_t launch_fwd(const FwdLaunch& l, cudaStream_t stream) {
+  if (l.args.bs_iter != nullptr) {
+    // block-sparse exists for fp16, head_dim <= 64, non-causal only (checked by the C ABI)
+    return l.is_dropout ? launch_one<64, false, false, true, true>(l, stream)
+                        : launch_one<64, false, false, false, true>(l, stream);
+  }
   return l.dpad == 64 ? launch_d<64>(l, stream) : launch_d<128>(l, stream);
 }
 

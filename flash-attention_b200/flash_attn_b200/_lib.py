@@ -19,6 +19,7 @@ EXPORTED_SYMBOLS = (
     "fa_fwd",
     "fa_bwd",
     "fa_bwd_workspace_bytes",
+    "fa_blocksparse_workspace_bytes",
     "fa_philox_increment",
     "fa_mask_block_n",
     "fa_debug_dropout_mask",
@@ -67,6 +68,10 @@ class FwdParams(ctypes.Structure):
         ("mask_heads_total", ctypes.c_int32),
         ("mask_head_offset", ctypes.c_int32),
         ("status", ctypes.c_void_p),
+        ("bs_workspace", ctypes.c_void_p),
+        ("bs_workspace_bytes", ctypes.c_size_t),
+        ("blockmask_rows", ctypes.c_int32),
+        ("blockmask_cols", ctypes.c_int32),
     ]
 
 
@@ -103,6 +108,8 @@ def _load():
     lib.fa_bwd.restype = ctypes.c_int
     lib.fa_bwd_workspace_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.fa_bwd_workspace_bytes.restype = ctypes.c_size_t
+    lib.fa_blocksparse_workspace_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
+    lib.fa_blocksparse_workspace_bytes.restype = ctypes.c_size_t
     lib.fa_philox_increment.argtypes = [ctypes.c_int32] * 4
     lib.fa_philox_increment.restype = ctypes.c_uint64
     lib.fa_mask_block_n.argtypes = [ctypes.c_int32] * 3

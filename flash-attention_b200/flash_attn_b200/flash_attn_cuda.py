@@ -107,31 +107,87 @@ def _round_up(x, m):
     return (x + m - 1) // m * m
 
 
-def fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale,
-        zero_tensors, is_causal, return_softmax, gen=None):
-    """mha_fwd (csrc/flash_attn/fmha_api.cpp:173-299): returns [o, softmax_lse(, s)]."""
+def _bs_workspace(device, batch, blockmask):
+    nbytes = lib.fa_blocksparse_workspace_bytes(batch, blockmask.shape[0], blockmask.shape[1])
+    return torch.empty(max(nbytes, 4), dtype=torch.uint8, device=device)
+
+
+def _check_blockmask(blockmask, max_seqlen_q, max_seqlen_k, q):
+    _require(blockmask.is_cuda and blockmask.dtype == torch.int32 and blockmask.is_contiguous(),
+             "blockmask must be a contiguous int32 CUDA tensor")
+    # The reference checks for exactly (ceil(max_k / 256), ceil16(max_q) / 16)
+    # (csrc/flash_attn/fmha_api.cpp:515); its own module passes a mask cut at a multiple of 256
+    # rows' worth of slots, so a larger mask is accepted here and its real row length is used.
+    want = (_round_up(int(max_seqlen_k), 256) // 256, _round_up(int(max_seqlen_q), 16) // 16)
+    _require(blockmask.dim() == 2 and blockmask.shape[0] >= want[0] and blockmask.shape[1] >= want[1],
+             "blockmask must have at least shape %s, got %s" % (want, tuple(blockmask.shape)))
+    _require(q.dtype == torch.float16, "block-sparse attention is fp16 only")
+    _require(q.shape[-1] in (16, 32, 64), "block-sparse attention supports head_dim 16, 32, 64")
+
+
+def _run_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout,
+             softmax_scale, zero_tensors, is_causal, return_softmax, gen, blockmask=None):
     batch, total_q, total_k, heads, d = _check_qkv(q, k, v, cu_seqlens_q, cu_seqlens_k)
     _require(p_dropout < 1.0, "p_dropout must be < 1")
     if return_softmax:
         raise RuntimeError("fa_b200: return_softmax is not available")
+    sparse = blockmask is not None
+    if sparse:
+        _require(not is_causal, "block-sparse attention does not support causal")
+        _check_blockmask(blockmask, max_seqlen_q, max_seqlen_k, q)
     with torch.cuda.device(q.device):
         lse_len = _round_up(int(max_seqlen_q), 16)
-        if zero_tensors:
+        if zero_tensors or sparse:  # the block-sparse entry always starts from o = 0 (:519)
             o = torch.zeros((total_q, heads, d), dtype=q.dtype, device=q.device)
+        else:
+            o = torch.empty((total_q, heads, d), dtype=q.dtype, device=q.device)
+        if zero_tensors:
             lse = torch.full((batch, heads, lse_len), float("-inf"), dtype=torch.float32,
                              device=q.device)
         else:
-            o = torch.empty((total_q, heads, d), dtype=q.dtype, device=q.device)
             lse = torch.empty((batch, heads, lse_len), dtype=torch.float32, device=q.device)
         seed, offset = 0, 0
         if p_dropout > 0:
-            inc = lib.fa_philox_increment(d, int(max_seqlen_q), int(max_seqlen_k), 0)
+            inc = lib.fa_philox_increment(d, int(max_seqlen_q), int(max_seqlen_k), int(sparse))
             seed, offset = _philox_state(gen, inc)
         p = FwdParams()
         _fill_fwd(p, q, k, v, o, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
                   p_dropout, softmax_scale, is_causal, seed, offset)
+        if sparse:
+            ws = _bs_workspace(q.device, batch, blockmask)
+            p.blockmask = blockmask.data_ptr()
+            p.blockmask_rows, p.blockmask_cols = blockmask.shape
+            p.bs_workspace, p.bs_workspace_bytes = ws.data_ptr(), ws.numel()
         check(lib.fa_fwd(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return [o, lse]
+
+
+def fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale,
+        zero_tensors, is_causal, return_softmax, gen=None):
+    """mha_fwd (csrc/flash_attn/fmha_api.cpp:173-299): returns [o, softmax_lse(, s)]."""
+    return _run_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout,
+                    softmax_scale, zero_tensors, is_causal, return_softmax, gen)
+
+
+def fwd_block(*args):
+    """mha_fwd_block.  Two call forms are accepted because the reference's Python call site and its
+    C++ signature disagree:
+      * 13 arguments, the C++ signature (csrc/flash_attn/fmha_api.cpp:451-464):
+        (q, k, v, cu_seqlens_q, cu_seqlens_k, blockmask, max_seqlen_q, max_seqlen_k, p_dropout,
+         softmax_scale, is_causal, return_softmax, gen) -> [o, softmax_lse]
+      * 9 arguments, the Python call site (flash_attn/flash_blocksparse_attn_interface.py:45-47):
+        (qkv, cu_seqlens, blockmask, dropout_p, max_s, softmax_scale, causal, return_softmax, gen)
+        with qkv (total, 3, heads, d) -> [context, softmax_lse]"""
+    if len(args) == 13:
+        (q, k, v, cu_q, cu_k, blockmask, max_q, max_k, p_dropout, scale, causal, ret_sm, gen) = args
+        return _run_fwd(q, k, v, cu_q, cu_k, max_q, max_k, p_dropout, scale, False, causal, ret_sm,
+                        gen, blockmask=blockmask)
+    if len(args) == 9:
+        (qkv, cu, blockmask, p_dropout, max_s, scale, causal, ret_sm, gen) = args
+        _require(qkv.dim() == 4 and qkv.shape[1] == 3, "qkv must be (total, 3, heads, head_dim)")
+        return _run_fwd(qkv[:, 0], qkv[:, 1], qkv[:, 2], cu, cu, max_s, max_s, p_dropout, scale,
+                        False, causal, ret_sm, gen, blockmask=blockmask)
+    raise TypeError("fwd_block takes 9 or 13 positional arguments, got %d" % len(args))
 
 
 _workspaces = {}
@@ -148,7 +204,8 @@ def _workspace(device, nbytes):
 
 
 def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
-        max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, gen=None, _stage_mask=0):
+        max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, gen=None, _stage_mask=0,
+        _blockmask=None):
     """mha_bwd (csrc/flash_attn/fmha_api.cpp:302-449): writes dq, dk, dv in place and returns
     [dq, dk, dv, softmax_d]."""
     batch, total_q, total_k, heads, d = _check_qkv(q, k, v, cu_seqlens_q, cu_seqlens_k)
@@ -189,6 +246,13 @@ def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
         p.dq_row_stride, p.dq_head_stride = dq.stride(0), dq.stride(1)
         p.dk_row_stride, p.dk_head_stride = dk.stride(0), dk.stride(1)
         p.dv_row_stride, p.dv_head_stride = dv.stride(0), dv.stride(1)
+        if _blockmask is not None:
+            _require(not is_causal, "block-sparse attention does not support causal")
+            _check_blockmask(_blockmask, max_seqlen_q, max_seqlen_k, q)
+            bws = _bs_workspace(q.device, batch, _blockmask)
+            p.fwd.blockmask = _blockmask.data_ptr()
+            p.fwd.blockmask_rows, p.fwd.blockmask_cols = _blockmask.shape
+            p.fwd.bs_workspace, p.fwd.bs_workspace_bytes = bws.data_ptr(), bws.numel()
         nbytes = lib.fa_bwd_workspace_bytes(total_q, heads, d)
         ws = _workspace(q.device, nbytes)
         p.workspace = ws.data_ptr()
@@ -196,3 +260,30 @@ def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
         p.stage_mask = _stage_mask
         check(lib.fa_bwd(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return [dq, dk, dv, softmax_d]
+
+
+def bwd_block(*args):
+    """mha_bwd_block.  Accepts the C++ signature (18 arguments,
+    csrc/flash_attn/fmha_api.cpp:575-594):
+        (dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k, blockmask,
+         max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, is_causal, gen)
+        -> [dq, dk, dv, softmax_d]
+    and the Python call site's form (12 arguments,
+    flash_attn/flash_blocksparse_attn_interface.py:56-58):
+        (dout, qkv, out, S_dmask, softmax_lse, cu_seqlens, blockmask, dropout_p, softmax_scale,
+         max_s, causal, gen) -> (dqkv, dp, softmax_d)
+    where S_dmask is ignored (the call site passes a placeholder) and dp is None."""
+    if len(args) == 18:
+        (dout, q, k, v, out, lse, dq, dk, dv, cu_q, cu_k, blockmask, max_q, max_k, p_dropout, scale,
+         causal, gen) = args
+        return bwd(dout, q, k, v, out, lse, dq, dk, dv, cu_q, cu_k, max_q, max_k, p_dropout, scale,
+                   False, causal, gen, _blockmask=blockmask)
+    if len(args) == 12:
+        (dout, qkv, out, _s_dmask, lse, cu, blockmask, p_dropout, scale, max_s, causal, gen) = args
+        _require(qkv.dim() == 4 and qkv.shape[1] == 3, "qkv must be (total, 3, heads, head_dim)")
+        dqkv = torch.empty_like(qkv)
+        res = bwd(dout.contiguous(), qkv[:, 0], qkv[:, 1], qkv[:, 2], out, lse, dqkv[:, 0],
+                  dqkv[:, 1], dqkv[:, 2], cu, cu, max_s, max_s, p_dropout, scale, False, causal, gen,
+                  _blockmask=blockmask)
+        return dqkv, None, res[3]
+    raise TypeError("bwd_block takes 12 or 18 positional arguments, got %d" % len(args))

@@ -36,13 +36,13 @@ def all_gather_heads(x_shard, group=None, async_op=False):
     wait for the collective and complete the local re-layout."""
     world = dist.get_world_size(group)
     total, hs, d = x_shard.shape
-    staging = torch.empty((world, total, hs, d), dtype=x_shard.dtype, device=x_shard.device)
+    staging = torch.empty((world * total, hs, d), dtype=x_shard.dtype, device=x_shard.device)
     work = dist.all_gather_into_tensor(staging, x_shard.contiguous(), group=group, async_op=async_op)
 
     def finish():
         if work is not None:
             work.wait()
-        return staging.permute(1, 0, 2, 3).reshape(total, world * hs, d)
+        return staging.view(world, total, hs, d).permute(1, 0, 2, 3).reshape(total, world * hs, d)
 
     if async_op:
         return None, finish

@@ -43,8 +43,10 @@ typedef struct fa_fwd_params {
   float* softmax_lse;
   const int32_t* cu_seqlens_q;
   const int32_t* cu_seqlens_k;
-  /* Block-sparse only (fmha_api.cpp:451-573): converted block mask [max_seqlen_k_rounded/256,
-   * max_seqlen_q_rounded/16] int32 as produced by convert_blockmask; NULL for dense attention. */
+  /* Block-sparse only (fmha_api.cpp:451-573): converted block mask, int32
+   * [blockmask_rows, blockmask_cols] as produced by convert_blockmask, with
+   * blockmask_rows >= ceil(max_seqlen_k / 256) key blocks and
+   * blockmask_cols >= ceil(max_seqlen_q / 16) list slots; NULL for dense attention. */
   const int32_t* blockmask;
   /* Optional [batch, heads, s_rows, s_cols] 16-bit output of the softmax probabilities with the
    * sign bit marking dropped entries (return_softmax); NULL to skip. */
@@ -71,6 +73,11 @@ typedef struct fa_fwd_params {
   int32_t mask_heads_total, mask_head_offset;
   /* Optional device int32[4]: a kernel that abandons a bounded wait writes a non-zero code here. */
   int32_t* status;
+  /* Block-sparse only: device scratch of fa_blocksparse_workspace_bytes() for the per-sequence
+   * block-visit table the call derives from blockmask and cu_seqlens. */
+  void* bs_workspace;
+  size_t bs_workspace_bytes;
+  int32_t blockmask_rows, blockmask_cols;
 } fa_fwd_params;
 
 /* Backward arguments: replaces FMHA_dgrad_params (csrc/flash_attn/src/fmha.h:141-163) as filled
@@ -105,6 +112,11 @@ int fa_bwd(const fa_bwd_params* params, void* cuda_stream);
 /* Size of the scratch fa_bwd needs: replaces the dq_tmp allocation of mha_bwd
  * (csrc/flash_attn/fmha_api.cpp:402-404). */
 size_t fa_bwd_workspace_bytes(int32_t total_q, int32_t heads, int32_t head_dim);
+
+/* Scratch a block-sparse call needs (fa_fwd_params.bs_workspace): one int32 per (batch entry,
+ * blockmask row, blockmask column).  The reference keeps this walk implicit in its kernels
+ * (csrc/flash_attn/src/fmha_block_fprop_kernel_1xN.h:205-232). */
+size_t fa_blocksparse_workspace_bytes(int32_t batch, int32_t blockmask_rows, int32_t blockmask_cols);
 
 /* Generator increment the caller must apply after a forward with dropout: replaces the
  * counter_offset computed in run_fmha_fp16_sm80_loop_ (fmha_fprop_fp16_kernel.sm80.cu:44-54). */
