@@ -306,4 +306,125 @@ int fa_bwd(const fa_bwd_params* p, void* cuda_stream) {
   return FA_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Backward without a caller-supplied workspace.
+//
+// The fp32 dQ accumulator of the backward pass normally lives in scratch the caller allocates
+// (fa_bwd_params.workspace).  Some callers have nothing to allocate it from: a serving process
+// whose device memory was carved up at start-up and that must stay away from the CUDA allocator
+// afterwards (cudaMalloc may fail once another pool owns the memory, and it synchronises the
+// device), or a plain C / Go / Java binding that holds tensors but no caching allocator to borrow
+// scratch from.  For them the accumulator below is part of the library image: every GPU that
+// loads the library holds these FA_STATIC_SCRATCH_BYTES until the process exits.
+static __device__ __align__(256) float g_static_dq_accum[FA_STATIC_SCRATCH_BYTES / sizeof(float)];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+float* g_static_dq_ptr[kMaxDevices] = {};
+
+// Device address of g_static_dq_accum on the current device.  The array's name is only a
+// host-side handle here; the kernels need the address cudaGetSymbolAddress reports, which differs
+// per device.  Looked up once per device (with that device current) and cached.
+int static_scratch_address(float** out) {
+  int dev = 0;
+  FA_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(FA_ERR_UNSUPPORTED, "device ordinal out of range");
+  // Binds the primary context to this thread without allocating anything.
+  FA_CUDA(cudaSetDevice(dev));
+  float* ptr = __atomic_load_n(&g_static_dq_ptr[dev], __ATOMIC_ACQUIRE);
+  if (ptr == nullptr) {
+    void* sym = nullptr;
+    FA_CUDA(cudaGetSymbolAddress(&sym, g_static_dq_accum));
+    if (sym == nullptr) return fail(FA_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    ptr = static_cast<float*>(sym);
+    __atomic_store_n(&g_static_dq_ptr[dev], ptr, __ATOMIC_RELEASE);
+  }
+  *out = ptr;
+  return FA_OK;
+}
+
+// make_tile_map without the context-binding cudaFree (static_scratch_address already bound it).
+int encode_tile_map(CUtensorMap* tm, const void* base, bool bf16, int64_t rows, int heads, int head_dim,
+                    int64_t row_stride, int64_t head_stride) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  FA_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "tensor base must be 16-byte aligned");
+  FA_REQUIRE((row_stride * 2) % 16 == 0 && (head_stride * 2) % 16 == 0,
+             "row and head strides must be multiples of 8 elements");
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(rows),
+                        static_cast<cuuint64_t>(heads)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_stride) * 2, static_cast<cuuint64_t>(head_stride) * 2};
+  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  return FA_OK;
+}
+
+}  // namespace
+
+int fa_bwd_static_scratch(const fa_bwd_params* p, void* cuda_stream) {
+  FA_REQUIRE(p != nullptr, "params is null");
+  const fa_fwd_params* f = &p->fwd;
+  if (int rc = validate_common(f)) return rc;
+  FA_REQUIRE(f->o && f->softmax_lse, "out and softmax_lse must be non-null");
+  FA_REQUIRE(p->dout && p->dq && p->dk && p->dv && p->softmax_d, "dout, dq, dk, dv, softmax_d must be non-null");
+  FA_REQUIRE(((reinterpret_cast<uintptr_t>(p->dq) | reinterpret_cast<uintptr_t>(p->dk) |
+               reinterpret_cast<uintptr_t>(p->dv) | reinterpret_cast<uintptr_t>(f->o)) & 15) == 0,
+             "o, dq, dk, dv must be 16-byte aligned");
+  FA_REQUIRE(p->dq_row_stride % 8 == 0 && p->dq_head_stride % 8 == 0 && p->dk_row_stride % 8 == 0 &&
+                 p->dk_head_stride % 8 == 0 && p->dv_row_stride % 8 == 0 && p->dv_head_stride % 8 == 0 &&
+                 f->o_row_stride % 8 == 0 && f->o_head_stride % 8 == 0,
+             "gradient strides must be multiples of 8 elements");
+  const size_t need = fa_bwd_workspace_bytes(f->total_q, f->heads, f->head_dim);
+  if (need > FA_STATIC_SCRATCH_BYTES)
+    return fail(FA_ERR_WORKSPACE,
+                "fa_bwd_static_scratch: this call needs " + std::to_string(need) +
+                    " bytes of dQ accumulator but the built-in scratch holds " +
+                    std::to_string(static_cast<size_t>(FA_STATIC_SCRATCH_BYTES)) +
+                    " (total_q * heads * padded head_dim * 4); use fa_bwd with a workspace");
+  float* accum = nullptr;
+  if (int rc = static_scratch_address(&accum)) return rc;
+
+  fa::BwdLaunch l;
+  std::memset(&l, 0, sizeof(l));
+  fill_args(f, &l.args.k);
+  if (f->blockmask)
+    if (int rc = setup_blocksparse(f, &l.args.k, static_cast<cudaStream_t>(cuda_stream))) return rc;
+  l.dpad = f->head_dim <= 64 ? 64 : 128;
+  l.is_bf16 = f->is_bf16 != 0;
+  l.is_causal = f->is_causal != 0;
+  l.is_dropout = f->p_dropout > 0.f;
+  l.stage_mask = 0;  // all three stages: the preprocess stage clears the rows of the shared scratch it uses
+  fa::BwdArgs& a = l.args;
+  a.o_in = f->o;
+  a.dout = p->dout;
+  a.do_row_stride = static_cast<int64_t>(f->heads) * f->head_dim;
+  a.do_head_stride = f->head_dim;
+  a.dq = p->dq; a.dk = p->dk; a.dv = p->dv;
+  a.dq_row_stride = p->dq_row_stride; a.dq_head_stride = p->dq_head_stride;
+  a.dk_row_stride = p->dk_row_stride; a.dk_head_stride = p->dk_head_stride;
+  a.dv_row_stride = p->dv_row_stride; a.dv_head_stride = p->dv_head_stride;
+  a.softmax_d = p->softmax_d;
+  a.dq_accum = accum;
+  a.total_q = f->total_q; a.total_k = f->total_k;
+  a.max_seqlen_q = f->max_seqlen_q; a.max_seqlen_k = f->max_seqlen_k;
+  a.p_keep = 1.f - f->p_dropout;
+  if (int rc = encode_tile_map(&l.tm_q, f->q, l.is_bf16, f->total_q, f->heads, f->head_dim,
+                               f->q_row_stride, f->q_head_stride)) return rc;
+  if (int rc = encode_tile_map(&l.tm_k, f->k, l.is_bf16, f->total_k, f->heads, f->head_dim,
+                               f->k_row_stride, f->k_head_stride)) return rc;
+  if (int rc = encode_tile_map(&l.tm_v, f->v, l.is_bf16, f->total_k, f->heads, f->head_dim,
+                               f->v_row_stride, f->v_head_stride)) return rc;
+  if (int rc = encode_tile_map(&l.tm_do, p->dout, l.is_bf16, f->total_q, f->heads, f->head_dim,
+                               a.do_row_stride, a.do_head_stride)) return rc;
+  FA_CUDA(fa::launch_bwd(l, static_cast<cudaStream_t>(cuda_stream)));
+  return FA_OK;
+}
+
 }  // extern "C"

@@ -14,10 +14,12 @@ FA_ERR_INVALID_ARGUMENT = -1
 FA_ERR_CUDA = -2
 FA_ERR_UNSUPPORTED = -3
 FA_ERR_WORKSPACE = -4
+FA_STATIC_SCRATCH_BYTES = 8 << 20
 
 EXPORTED_SYMBOLS = (
     "fa_fwd",
     "fa_bwd",
+    "fa_bwd_static_scratch",
     "fa_bwd_workspace_bytes",
     "fa_blocksparse_workspace_bytes",
     "fa_philox_increment",
@@ -106,6 +108,8 @@ def _load():
     lib.fa_fwd.restype = ctypes.c_int
     lib.fa_bwd.argtypes = [ctypes.POINTER(BwdParams), ctypes.c_void_p]
     lib.fa_bwd.restype = ctypes.c_int
+    lib.fa_bwd_static_scratch.argtypes = [ctypes.POINTER(BwdParams), ctypes.c_void_p]
+    lib.fa_bwd_static_scratch.restype = ctypes.c_int
     lib.fa_bwd_workspace_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.fa_bwd_workspace_bytes.restype = ctypes.c_size_t
     lib.fa_blocksparse_workspace_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]

@@ -109,6 +109,26 @@ int fa_fwd(const fa_fwd_params* params, void* cuda_stream);
  * (:575-718).  Writes dq, dk, dv and softmax_d. */
 int fa_bwd(const fa_bwd_params* params, void* cuda_stream);
 
+/* Capacity of the dQ accumulator built into the library for fa_bwd_static_scratch. */
+#define FA_STATIC_SCRATCH_BYTES (8u << 20)
+
+/* No counterpart in the reference.  Same computation and arguments as fa_bwd, for callers that
+ * cannot allocate device memory when they call (a serving process whose memory was partitioned at
+ * start-up and must not enter the CUDA allocator again, or a C / Go / Java binding with no caching
+ * allocator to borrow scratch from): `workspace` and `workspace_bytes` are ignored and the fp32 dQ
+ * accumulator is a fixed array inside the library image instead, FA_STATIC_SCRATCH_BYTES per GPU
+ * that loads the library, held until the process exits.
+ *   - Limit: total_q * heads * (head_dim <= 64 ? 64 : 128) * 4 <= FA_STATIC_SCRATCH_BYTES; larger
+ *     calls return FA_ERR_WORKSPACE and launch nothing.
+ *   - The call allocates and frees nothing (no cudaMalloc / cudaFree, no allocating library call).
+ *   - The first call on each device looks up the device address of the array and caches it; make
+ *     that first call before starting any stream capture on that device.
+ *   - All calls on a device share the one array.  Each call clears the rows it is about to use,
+ *     so the previous call's contents never leak into a result, but two calls that overlap on the
+ *     GPU (different streams, or different host threads on the same device) race on it: order them
+ *     on one stream or with events.  Block-sparse calls still need fwd.bs_workspace. */
+int fa_bwd_static_scratch(const fa_bwd_params* params, void* cuda_stream);
+
 /* Size of the scratch fa_bwd needs: replaces the dq_tmp allocation of mha_bwd
  * (csrc/flash_attn/fmha_api.cpp:402-404). */
 size_t fa_bwd_workspace_bytes(int32_t total_q, int32_t heads, int32_t head_dim);

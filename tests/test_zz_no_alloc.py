@@ -1,0 +1,88 @@
+"""fa_bwd_static_scratch: the backward entry point for callers that cannot allocate device memory
+at call time (the dQ accumulator is an array inside the library instead of caller scratch).
+
+Called through the C ABI twice in a row and compared with fa_bwd on the same inputs.  The second
+call uses a smaller problem, so it also shows that what the first call left in the shared array
+does not leak into the next result.  Collected last on purpose (file name): a failure here cannot
+hide the result of any other test in a run that stops at the first failure."""
+import ctypes
+
+import pytest
+import torch
+
+from tests import _util as U
+
+pytestmark = pytest.mark.gpu
+
+
+def _bwd_params(fc, _lib, q, k, v, out, lse, dout, grads, softmax_d, cu_q, cu_k, max_q, max_k, scale, causal):
+    p = _lib.BwdParams()
+    fc._fill_fwd(p.fwd, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, 0.0, scale, causal, 0, 0)
+    p.dout = dout.data_ptr()
+    p.dq, p.dk, p.dv = (g.data_ptr() for g in grads)
+    p.softmax_d = softmax_d.data_ptr()
+    p.dq_row_stride, p.dq_head_stride = grads[0].stride(0), grads[0].stride(1)
+    p.dk_row_stride, p.dk_head_stride = grads[1].stride(0), grads[1].stride(1)
+    p.dv_row_stride, p.dv_head_stride = grads[2].stride(0), grads[2].stride(1)
+    return p
+
+
+def _one_call(seqlens_q, seqlens_k, heads, d, dtype, causal, seed):
+    from flash_attn_b200 import _lib
+    from flash_attn_b200 import flash_attn_cuda as fc
+    q, k, v, dout, cu_q, cu_k = U.make_varlen(seqlens_q, seqlens_k, heads, d, dtype, seed=seed)
+    max_q, max_k = max(seqlens_q), max(seqlens_k)
+    scale = d ** -0.5
+    out, lse = fc.fwd(q, k, v, cu_q, cu_k, max_q, max_k, 0.0, scale, False, causal, False, None)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    # existing entry point, caller-allocated workspace
+    ref = [torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)]
+    d_ref = torch.empty_like(lse)
+    p = _bwd_params(fc, _lib, q, k, v, out, lse, dout, ref, d_ref, cu_q, cu_k, max_q, max_k, scale, causal)
+    ws = torch.empty(_lib.lib.fa_bwd_workspace_bytes(q.shape[0], heads, d), dtype=torch.uint8, device="cuda")
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+    _lib.check(_lib.lib.fa_bwd(ctypes.byref(p), stream))
+
+    # new entry point: no workspace passed, nothing allocated by the call
+    got = [torch.full_like(q, float("nan")), torch.full_like(k, float("nan")), torch.full_like(v, float("nan"))]
+    d_got = torch.empty_like(lse)
+    p2 = _bwd_params(fc, _lib, q, k, v, out, lse, dout, got, d_got, cu_q, cu_k, max_q, max_k, scale, causal)
+    p2.workspace, p2.workspace_bytes = None, 0
+    _lib.check(_lib.lib.fa_bwd_static_scratch(ctypes.byref(p2), stream))
+    torch.cuda.synchronize()
+    fc.check_device_status()
+
+    # dk, dv are computed in a fixed order: identical.  dq is summed with fp32 atomics whose order
+    # varies from run to run: same tolerance as the dense-vs-sparse comparison of the other tests.
+    assert torch.equal(got[1], ref[1]) and torch.equal(got[2], ref[2])
+    assert U.max_err(got[0], ref[0]) < 2e-3
+    assert not torch.isnan(got[0].float()).any()
+    for b, n in enumerate(seqlens_q):
+        assert torch.equal(d_got[b, :, :n], d_ref[b, :, :n])
+    # and both agree with the oracle
+    o32, dq32, dk32, dv32 = U.oracle_cpu(q, k, v, dout, cu_q, cu_k, scale, causal)
+    o16, dq16, dk16, dv16 = U.oracle_cpu(q, k, v, dout, cu_q, cu_k, scale, causal, dtype=dtype)
+    U.assert_within_2x("dq", got[0], dq32, dq16)
+    U.assert_within_2x("dk", got[1], dk32, dk16)
+    U.assert_within_2x("dv", got[2], dv32, dv16)
+
+
+def test_static_scratch_backward_two_calls_in_a_row():
+    _one_call([700, 300], [700, 300], 4, 64, torch.float16, True, seed=61)
+    _one_call([130], [257], 2, 128, torch.bfloat16, False, seed=62)
+
+
+def test_static_scratch_rejects_oversized_calls():
+    from flash_attn_b200 import _lib
+    from flash_attn_b200 import flash_attn_cuda as fc
+    heads, d = 16, 64
+    total = _lib.FA_STATIC_SCRATCH_BYTES // (heads * d * 4) + 1
+    q = torch.zeros(total, heads, d, device="cuda", dtype=torch.float16)
+    cu = torch.tensor([0, total], dtype=torch.int32, device="cuda")
+    lse = torch.zeros(1, heads, (total + 15) // 16 * 16, device="cuda")
+    grads = [torch.empty_like(q) for _ in range(3)]
+    p = _bwd_params(fc, _lib, q, q, q, q, lse, q, grads, torch.empty_like(lse), cu, cu, total, total, 0.125, False)
+    rc = _lib.lib.fa_bwd_static_scratch(ctypes.byref(p), None)
+    assert rc == _lib.FA_ERR_WORKSPACE
+    assert b"built-in scratch" in _lib.lib.fa_last_error()
