@@ -180,6 +180,8 @@ def main():
     ap.add_argument("--seqlen", type=int, default=4096)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="skip the host-buffer and CPU legs (for profiler runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -290,7 +292,7 @@ def main():
         out_host.copy_(out.detach(), non_blocking=True)
         dqkv_host.copy_(x.grad, non_blocking=True)
 
-    ms_e2e = timed(step_e2e, max(3, args.steps // 2), 3)
+    ms_e2e = timed(step_e2e, max(3, args.steps // 2), 3) if not args.kernels_only else float("nan")
     e2e_value = world * flops_step / (ms_e2e * 1e-3) / 1e12
     h2d = qkv_host.numel() * 2 + dout_host.numel() * 2
     d2h = out_host.numel() * 2 + dqkv_host.numel() * 2
@@ -336,7 +338,7 @@ def main():
         "roofline": roofline,
     }
 
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and not args.kernels_only:
         threads = os.cpu_count() or 1
         sample_len = min(max(lengths), 2048)
         dt, fl = cpu_attention_sample(sample_len, HEADS, HEAD_DIM, False, threads, repeats=2)

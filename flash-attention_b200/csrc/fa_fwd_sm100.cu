@@ -17,6 +17,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "fa_kernels.h"
+#include "fa_math.cuh"
 #include "sm100_prims.cuh"
 
 namespace fa {
@@ -25,7 +26,7 @@ namespace {
 
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
-constexpr int kFwdThreads = 320;
+constexpr int kFwdThreads = 384;  // 2 softmax warpgroups + 1 (producer, MMA issuer, 2 idle warps)
 
 template <int D>
 struct FwdCfg {
@@ -50,6 +51,15 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 template <bool BF16>
@@ -156,6 +166,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const uint32_t tmem = sh.tmem_base;
   volatile int* abort_flag = &sh.abort_flag;
 
+  if (warp >= 8) reg_dealloc<56>();
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -257,8 +268,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (has_next) mma_commit(smem_u32(&sh.k_empty[sn]));
       }
     }
-  } else {
+  } else if (warp < 8) {
     // ------------------------------------------------------------------ softmax groups
+    reg_alloc<224>();
     const int g = warp >> 2;
     const int row = tid & 127;
     const int ig = m0[g] + row;  // query index within the sequence
@@ -270,14 +282,22 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
+    const uint64_t c2 = pack_f2(a.scale_log2, a.scale_log2);
 
-    // dropout bookkeeping
+    // dropout bookkeeping: a lane and its partner 8 lanes away own rows r and r + 8 of one 16-row
+    // block, which share every Philox call; each computes half of the calls and they swap halves.
     const int64_t bh_sub =
         (static_cast<int64_t>(b) * a.drop.heads_total + a.drop.head_offset + h) * 256;
     const int L16 = (sq + 15) >> 4;
+    const bool hi_lane = (row & 8) != 0;
+    const uint32_t thr = a.drop.threshold;
+    const uint32_t thr_hi = (thr + 1u) << 16;
+    PhiloxKeys keys;
+    if constexpr (DROPOUT) keys.init(a.drop.key0, a.drop.key1);
 
     for (int j = 0; j < n && ok; ++j) {
       ok = mbar_wait(smem_u32(&sh.s_full[g]), j & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       uint32_t sr[4][32];
@@ -299,13 +319,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             if (!valid) sr[c][i] = __float_as_uint(-INFINITY);
           }
       }
+      int32_t bs_it = 0;
       if constexpr (BLOCKSPARSE) {
         // a 16-row block that is not in the layout for this 256-column key block sees -inf
         const int kb = col0 >> 8;
-        const int32_t it = (ig >> 4) < a.bs_rows16
-                               ? a.bs_iter[(static_cast<int64_t>(b) * a.bs_kblocks + kb) * a.bs_rows16 + (ig >> 4)]
-                               : -1;
-        if (it < 0) {
+        bs_it = (ig >> 4) < a.bs_rows16
+                    ? a.bs_iter[(static_cast<int64_t>(b) * a.bs_kblocks + kb) * a.bs_rows16 + (ig >> 4)]
+                    : -1;
+        if (bs_it < 0) {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
@@ -313,28 +334,37 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
       }
 
-      float mx = -INFINITY;
+      float mxa = -INFINITY, mxb = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[c][i]));
-      const float m_new = fmaxf(m_run, mx);
+        for (int i = 0; i < 32; i += 4) {
+          mxa = max3(mxa, __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+          mxb = max3(mxb, __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
+        }
+      const float m_new = max3(m_run, mxa, mxb);
 
       if (j > 0) {
         ok = mbar_wait(smem_u32(&sh.o_full[g]), (j - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
         const bool grow = m_new > m_run;
         if (__any_sync(0xffffffffu, grow)) {
-          const float alpha =
-              (m_new == -INFINITY) ? 1.f : fast_exp2((m_run - m_new) * a.scale_log2);
+          const float alpha = (m_new == -INFINITY) ? 1.f : ex2f((m_run - m_new) * a.scale_log2);
+          const uint64_t alpha2 = pack_f2(alpha, alpha);
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
             uint32_t orr[32];
             tmem_ld32(tO + c * 32, orr);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+            for (int i = 0; i < 32; i += 2) {
+              float lo, hi;
+              unpack_f2(mul2(pack_f2(__uint_as_float(orr[i]), __uint_as_float(orr[i + 1])), alpha2), lo, hi);
+              orr[i] = __float_as_uint(lo);
+              orr[i + 1] = __float_as_uint(hi);
+            }
             tmem_st32(tO + c * 32, orr);
           }
           l_run *= alpha;
@@ -342,51 +372,64 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
       m_run = m_new;
       const float mc = (m_new == -INFINITY) ? 0.f : m_new * a.scale_log2;
+      const uint64_t nmc2 = pack_f2(-mc, -mc);
 
-      float psum = 0.f;
+      // p = exp2(s * c - m * c): packed fma, one ex2 per element, packed row sum, 16-bit pack
+      uint32_t pk[64];
+      uint64_t sum_a = 0ull, sum_b = 0ull;
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float p = fast_exp2(fmaf(__uint_as_float(sr[c][i]), a.scale_log2, -mc));
-          psum += p;
-          sr[c][i] = __float_as_uint(p);
+        for (int i = 0; i < 32; i += 4) {
+          float p0, p1, p2, p3;
+          unpack_f2(fma2(pack_f2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), c2, nmc2), p0, p1);
+          unpack_f2(fma2(pack_f2(__uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3])), c2, nmc2), p2, p3);
+          p0 = ex2f(p0); p1 = ex2f(p1); p2 = ex2f(p2); p3 = ex2f(p3);
+          sum_a = add2(sum_a, pack_f2(p0, p1));
+          sum_b = add2(sum_b, pack_f2(p2, p3));
+          pk[c * 16 + i / 2] = pack_lowp<BF16>(p0, p1);
+          pk[c * 16 + i / 2 + 1] = pack_lowp<BF16>(p2, p3);
         }
-      l_run += psum;
+      {
+        float s0, s1;
+        unpack_f2(add2(sum_a, sum_b), s0, s1);
+        l_run += s0 + s1;
+      }
 
       if constexpr (DROPOUT) {
-        int64_t it_index;
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int hgrp = 0; hgrp < 2; ++hgrp) {
-            const int jg0 = col0 + c * 32 + hgrp * 16;
-            if constexpr (BLOCKSPARSE) {
-              it_index = (ig >> 4) < a.bs_rows16
-                             ? a.bs_iter[(static_cast<int64_t>(b) * a.bs_kblocks + (jg0 >> 8)) * a.bs_rows16 + (ig >> 4)]
-                             : 0;
-            } else {
-              it_index = fa_iter_index(CAUSAL, jg0 >> a.drop.n_shift, ig >> 4, L16, a.drop.n_shift);
-            }
-            const uint32_t keep = fa_dropout_keep16(a.drop, bh_sub, ig, jg0, it_index);
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              if (!((keep >> i) & 1u)) sr[c][hgrp * 16 + i] = 0u;
-          }
+        for (int grp = 0; grp < 8; ++grp) {
+          const int jg0 = col0 + grp * 16;
+          int64_t it_index;
+          if constexpr (BLOCKSPARSE) it_index = bs_it;
+          else it_index = fa_iter_index(CAUSAL, jg0 >> a.drop.n_shift, ig >> 4, L16, a.drop.n_shift);
+          uint32_t ca[4], cb[4];
+          const int q0 = hi_lane ? 2 : 0;
+          fa_philox_call(a.drop, keys, bh_sub, ig, jg0, q0, it_index, ca);
+          fa_philox_call(a.drop, keys, bh_sub, ig, jg0, q0 + 1, it_index, cb);
+          // words this row keeps from its own calls / words it hands to the partner row
+          const uint32_t ka0 = hi_lane ? ca[2] : ca[0], ka1 = hi_lane ? ca[3] : ca[1];
+          const uint32_t kb0 = hi_lane ? cb[2] : cb[0], kb1 = hi_lane ? cb[3] : cb[1];
+          const uint32_t ra0 = __shfl_xor_sync(0xffffffffu, hi_lane ? ca[0] : ca[2], 8);
+          const uint32_t ra1 = __shfl_xor_sync(0xffffffffu, hi_lane ? ca[1] : ca[3], 8);
+          const uint32_t rb0 = __shfl_xor_sync(0xffffffffu, hi_lane ? cb[0] : cb[2], 8);
+          const uint32_t rb1 = __shfl_xor_sync(0xffffffffu, hi_lane ? cb[1] : cb[3], 8);
+          // quarter q covers column pairs q (columns 2q, 2q+1) and q + 4 (columns 2q+8, 2q+9)
+          uint32_t* pg = pk + grp * 8;
+          pg[0] &= keep_mask_pair(hi_lane ? ra0 : ka0, thr, thr_hi);
+          pg[4] &= keep_mask_pair(hi_lane ? ra1 : ka1, thr, thr_hi);
+          pg[1] &= keep_mask_pair(hi_lane ? rb0 : kb0, thr, thr_hi);
+          pg[5] &= keep_mask_pair(hi_lane ? rb1 : kb1, thr, thr_hi);
+          pg[2] &= keep_mask_pair(hi_lane ? ka0 : ra0, thr, thr_hi);
+          pg[6] &= keep_mask_pair(hi_lane ? ka1 : ra1, thr, thr_hi);
+          pg[3] &= keep_mask_pair(hi_lane ? kb0 : rb0, thr, thr_hi);
+          pg[7] &= keep_mask_pair(hi_lane ? kb1 : rb1, thr, thr_hi);
+        }
       }
 
-      // pack to 16 bit and hand P to the tensor core through tensor memory
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t pr[32];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          pr[i] = pack2<BF16>(__uint_as_float(sr[2 * c][2 * i]), __uint_as_float(sr[2 * c][2 * i + 1]));
-          pr[16 + i] = pack2<BF16>(__uint_as_float(sr[2 * c + 1][2 * i]),
-                                   __uint_as_float(sr[2 * c + 1][2 * i + 1]));
-        }
-        tmem_st32(tS + c * 32, pr);
-      }
+      // hand P to the tensor core through tensor memory
+      tmem_st32(tS, reinterpret_cast<uint32_t(&)[32]>(pk[0]));
+      tmem_st32(tS + 32, reinterpret_cast<uint32_t(&)[32]>(pk[32]));
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(&sh.p_full[g]));
@@ -396,6 +439,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     if (active) {
       if (n > 0 && ok) {
         ok = mbar_wait(smem_u32(&sh.o_full[g]), (n - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
       }
       const bool bad_sum = (l_run == 0.f) || (l_run != l_run);
@@ -415,15 +459,15 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           for (int i = 0; i < 32; ++i) orr[i] = 0u;
         }
         if (store_row && c * 32 < a.head_dim) {
-          uint32_t pk[16];
+          uint32_t pko[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            pk[i] = pack2<BF16>(__uint_as_float(orr[2 * i]) * inv, __uint_as_float(orr[2 * i + 1]) * inv);
+            pko[i] = pack_lowp<BF16>(__uint_as_float(orr[2 * i]) * inv, __uint_as_float(orr[2 * i + 1]) * inv);
           uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
           const int nvec = min(4, (a.head_dim - c * 32) / 8);
 #pragma unroll
           for (int v = 0; v < 4; ++v)
-            if (v < nvec) dst[v] = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+            if (v < nvec) dst[v] = make_uint4(pko[4 * v], pko[4 * v + 1], pko[4 * v + 2], pko[4 * v + 3]);
         }
       }
       if (store_row) {
