@@ -43,6 +43,7 @@ def _digest(paths):
             h.update(p.encode())
             h.update(f.read())
     h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(os.environ.get("FA_PROFILE", "").encode())
     return h.hexdigest()
 
 
@@ -59,10 +60,11 @@ def build(force=False, verbose=False):
         return LIB_PATH
 
     nvcc = _nvcc()
+    extra = ["-DFA_PROFILE"] if os.environ.get("FA_PROFILE") else []
 
     def compile_one(src):
         obj = os.path.join(OBJ_DIR, os.path.basename(src).replace(".cu", ".o"))
-        cmd = [nvcc] + NVCC_FLAGS + ["-c", src, "-o", obj]
+        cmd = [nvcc] + NVCC_FLAGS + extra + ["-c", src, "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         log = os.path.join(OBJ_DIR, os.path.basename(src) + ".log")
         with open(log, "w") as f:

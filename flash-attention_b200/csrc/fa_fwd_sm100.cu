@@ -35,6 +35,11 @@ struct FwdCfg {
   static constexpr int kTileBytes = kBlockM * D * 2;
   static constexpr int kSmemBytes = (2 + 2 * kStages) * kTileBytes + 1024;
   static constexpr uint32_t kTmemS0 = 0, kTmemS1 = 128, kTmemO0 = 256, kTmemO1 = 256 + D;
+  // d = 64 leaves 128 tensor-memory columns free: P gets its own columns there, so the next
+  // S = Q K^T can be issued as soon as the softmax group has read the current S into registers.
+  // At d = 128 the 512 columns are full and P overwrites the first 64 columns of its S buffer.
+  static constexpr bool kSeparateP = (D == 64);
+  static constexpr uint32_t kTmemP0 = kSeparateP ? 384 : kTmemS0, kTmemP1 = kSeparateP ? 448 : kTmemS1;
 };
 
 constexpr int kMaxSparseTiles = 1024;  // key tiles of 128 per sequence in block-sparse mode
@@ -42,7 +47,7 @@ constexpr int kMaxSparseTiles = 1024;  // key tiles of 128 per sequence in block
 struct FwdShared {
   uint64_t q_full[2];
   uint64_t k_full[3], k_empty[3], v_full[3], v_empty[3];
-  uint64_t s_full[2], p_full[2], o_full[2];
+  uint64_t s_full[2], s_free[2], p_full[2], o_full[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -52,6 +57,19 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+
+// Optional cycle accounting (build with -DFA_PROFILE): thread 0 of softmax group 0 and the MMA
+// thread of CTA (0,0,0) accumulate the cycles they spend in each phase into status[8..].
+#ifdef FA_PROFILE
+#define FA_PROF_DECL long long prof_t = clock64(); long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define FA_PROF(slot) { const long long now_ = clock64(); prof_acc[slot] += now_ - prof_t; prof_t = now_; }
+#define FA_PROF_FLUSH(base, n) if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && a.status) { \
+    for (int i_ = 0; i_ < 8; ++i_) a.status[(base) + i_] = static_cast<int32_t>(prof_acc[i_] / ((n) > 0 ? (n) : 1)); }
+#else
+#define FA_PROF_DECL
+#define FA_PROF(slot)
+#define FA_PROF_FLUSH(base, n)
+#endif
 
 template <int N>
 __device__ __forceinline__ void reg_alloc() {
@@ -148,6 +166,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&sh.q_full[i]), 1);
       mbar_init(smem_u32(&sh.s_full[i]), 1);
+      mbar_init(smem_u32(&sh.s_free[i]), kBlockM);
       mbar_init(smem_u32(&sh.p_full[i]), kBlockM);
       mbar_init(smem_u32(&sh.o_full[i]), 1);
     }
@@ -213,6 +232,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       constexpr uint32_t idesc_pv = make_idesc(BF16, false, true, kBlockM, D);
       const uint32_t tS[2] = {tmem + Cfg::kTmemS0, tmem + Cfg::kTmemS1};
       const uint32_t tO[2] = {tmem + Cfg::kTmemO0, tmem + Cfg::kTmemO1};
+      const uint32_t tP[2] = {tmem + Cfg::kTmemP0, tmem + Cfg::kTmemP1};
       auto issue_qk = [&](int g, int stage) {
         const uint32_t qa = smem_q + g * Cfg::kTileBytes;
         const uint32_t ka = smem_k + stage * Cfg::kTileBytes;
@@ -228,7 +248,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const uint32_t va = smem_v + stage * Cfg::kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < kBlockN / 16; ++ks) {
-          mma_ts(tO[g], tS[g] + ks * 8, make_smem_desc(va + ks * 2048, 16384, 1024), idesc_pv,
+          mma_ts(tO[g], tP[g] + ks * 8, make_smem_desc(va + ks * 2048, 16384, 1024), idesc_pv,
                  accumulate || ks > 0);
         }
         mma_commit(smem_u32(&sh.o_full[g]));
@@ -246,26 +266,75 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           mma_commit(smem_u32(&sh.k_empty[0]));
         }
       }
+      FA_PROF_DECL
       for (int j = 0; j < n_max && ok; ++j) {
         const int s = j % Cfg::kStages;
         const int sn = (j + 1) % Cfg::kStages;
         const bool has_next = j + 1 < n_max;
-        ok = mbar_wait(smem_u32(&sh.v_full[s]), (j / Cfg::kStages) & 1, abort_flag);
+        FA_PROF(0)
+        if (!Cfg::kSeparateP) ok = mbar_wait(smem_u32(&sh.v_full[s]), (j / Cfg::kStages) & 1, abort_flag);
         if (ok && has_next)
           ok = mbar_wait(smem_u32(&sh.k_full[sn]), ((j + 1) / Cfg::kStages) & 1, abort_flag);
+        if (!ok) break;
+        FA_PROF(1)
+        if constexpr (Cfg::kSeparateP) {
+          // this warp issues only the score products; warp 10 issues P*V
+          for (int g = 0; g < 2; ++g) {
+            if (j + 1 < n_tiles[g]) {
+              ok = mbar_wait(smem_u32(&sh.s_free[g]), j & 1, abort_flag);
+              if (!ok) break;
+              tc_fence_after();
+              issue_qk(g, sn);
+            }
+          }
+          if (!ok) break;
+          FA_PROF(5)
+        } else {
+          for (int g = 0; g < 2; ++g) {
+            if (j < n_tiles[g]) {
+              ok = mbar_wait(smem_u32(&sh.p_full[g]), j & 1, abort_flag);
+              if (!ok) break;
+              FA_PROF(2 + g)
+              tc_fence_after();
+              issue_pv(g, s, j > 0);
+              FA_PROF(4)
+              if (j + 1 < n_tiles[g]) issue_qk(g, sn);
+              FA_PROF(5)
+            }
+          }
+        }
+        if (!ok) break;
+        if (!Cfg::kSeparateP) mma_commit(smem_u32(&sh.v_empty[s]));
+        if (has_next) mma_commit(smem_u32(&sh.k_empty[sn]));
+      }
+      FA_PROF_FLUSH(16, n_max)
+    }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------------ second MMA issuer (d = 64): P*V
+    if (Cfg::kSeparateP && lane == 0) {
+      constexpr uint32_t idesc_pv = make_idesc(BF16, false, true, kBlockM, D);
+      const uint32_t tO[2] = {tmem + Cfg::kTmemO0, tmem + Cfg::kTmemO1};
+      const uint32_t tP[2] = {tmem + Cfg::kTmemP0, tmem + Cfg::kTmemP1};
+      bool ok = true;
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int s = j % Cfg::kStages;
+        ok = mbar_wait(smem_u32(&sh.v_full[s]), (j / Cfg::kStages) & 1, abort_flag);
         if (!ok) break;
         for (int g = 0; g < 2; ++g) {
           if (j < n_tiles[g]) {
             ok = mbar_wait(smem_u32(&sh.p_full[g]), j & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            issue_pv(g, s, j > 0);
-            if (j + 1 < n_tiles[g]) issue_qk(g, sn);
+            const uint32_t va = smem_v + s * Cfg::kTileBytes;
+#pragma unroll
+            for (int ks = 0; ks < kBlockN / 16; ++ks)
+              mma_ts(tO[g], tP[g] + ks * 8, make_smem_desc(va + ks * 2048, 16384, 1024), idesc_pv,
+                     j > 0 || ks > 0);
+            mma_commit(smem_u32(&sh.o_full[g]));
           }
         }
         if (!ok) break;
         mma_commit(smem_u32(&sh.v_empty[s]));
-        if (has_next) mma_commit(smem_u32(&sh.k_empty[sn]));
       }
     }
   } else if (warp < 8) {
@@ -277,6 +346,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + (g == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1) + lane_sel;
     const uint32_t tO = tmem + (g == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1) + lane_sel;
+    const uint32_t tP = tmem + (g == 0 ? Cfg::kTmemP0 : Cfg::kTmemP1) + lane_sel;
     const int n = n_tiles[g];
     const bool active = m0[g] < sq;
 
@@ -295,15 +365,23 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     PhiloxKeys keys;
     if constexpr (DROPOUT) keys.init(a.drop.key0, a.drop.key1);
 
+    FA_PROF_DECL
     for (int j = 0; j < n && ok; ++j) {
+      FA_PROF(0)
       ok = mbar_wait(smem_u32(&sh.s_full[g]), j & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      FA_PROF(1)
       tc_fence_after();
       uint32_t sr[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sr[c]);
       tmem_wait_ld();
+      if constexpr (Cfg::kSeparateP) {
+        tc_fence_before();
+        mbar_arrive(smem_u32(&sh.s_free[g]));
+      }
+      FA_PROF(2)
 
       const int col0 = kv_tile(j) * kBlockN;
       bool need_mask = (col0 + kBlockN > sk);
@@ -343,35 +421,16 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           mxb = max3(mxb, __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
         }
       const float m_new = max3(m_run, mxa, mxb);
+      FA_PROF(3)
 
-      if (j > 0) {
-        ok = mbar_wait(smem_u32(&sh.o_full[g]), (j - 1) & 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-        const bool grow = m_new > m_run;
-        if (__any_sync(0xffffffffu, grow)) {
-          const float alpha = (m_new == -INFINITY) ? 1.f : ex2f((m_run - m_new) * a.scale_log2);
-          const uint64_t alpha2 = pack_f2(alpha, alpha);
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t orr[32];
-            tmem_ld32(tO + c * 32, orr);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              float lo, hi;
-              unpack_f2(mul2(pack_f2(__uint_as_float(orr[i]), __uint_as_float(orr[i + 1])), alpha2), lo, hi);
-              orr[i] = __float_as_uint(lo);
-              orr[i + 1] = __float_as_uint(hi);
-            }
-            tmem_st32(tO + c * 32, orr);
-          }
-          l_run *= alpha;
-        }
-      }
-      m_run = m_new;
-      const float mc = (m_new == -INFINITY) ? 0.f : m_new * a.scale_log2;
+      // The running max is only raised when it would grow by more than 2^8 in the exponent:
+      // until then the stale max keeps every p below 256 and saves rescaling O.
+      const bool grow = (m_new - m_run) * a.scale_log2 > 8.f;
+      const float m_next = grow ? m_new : m_run;
+      const float alpha = (!grow || m_run == -INFINITY) ? (grow ? 0.f : 1.f) : ex2f((m_run - m_new) * a.scale_log2);
+      m_run = m_next;
+      FA_PROF(4)
+      const float mc = (m_next == -INFINITY) ? 0.f : m_next * a.scale_log2;
       const uint64_t nmc2 = pack_f2(-mc, -mc);
 
       // p = exp2(s * c - m * c): packed fma, one ex2 per element, packed row sum, 16-bit pack
@@ -393,9 +452,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       {
         float s0, s1;
         unpack_f2(add2(sum_a, sum_b), s0, s1);
-        l_run += s0 + s1;
+        l_run = l_run * alpha + (s0 + s1);
       }
 
+      FA_PROF(5)
       if constexpr (DROPOUT) {
 #pragma unroll
         for (int grp = 0; grp < 8; ++grp) {
@@ -427,13 +487,40 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
       }
 
+      FA_PROF(6)
+      // P*V of the previous tile must have finished before O is rescaled or its P buffer reused
+      if (j > 0) {
+        ok = mbar_wait(smem_u32(&sh.o_full[g]), (j - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, grow)) {
+          const uint64_t alpha2 = pack_f2(alpha, alpha);
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t orr[32];
+            tmem_ld32(tO + c * 32, orr);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float lo, hi;
+              unpack_f2(mul2(pack_f2(__uint_as_float(orr[i]), __uint_as_float(orr[i + 1])), alpha2), lo, hi);
+              orr[i] = __float_as_uint(lo);
+              orr[i + 1] = __float_as_uint(hi);
+            }
+            tmem_st32(tO + c * 32, orr);
+          }
+        }
+      }
       // hand P to the tensor core through tensor memory
-      tmem_st32(tS, reinterpret_cast<uint32_t(&)[32]>(pk[0]));
-      tmem_st32(tS + 32, reinterpret_cast<uint32_t(&)[32]>(pk[32]));
+      tmem_st32(tP, reinterpret_cast<uint32_t(&)[32]>(pk[0]));
+      tmem_st32(tP + 32, reinterpret_cast<uint32_t(&)[32]>(pk[32]));
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(&sh.p_full[g]));
+      FA_PROF(7)
     }
+    if (g == 0 && row == 0) { FA_PROF_FLUSH(8, n) }
 
     // ---------------- epilogue: O = acc / (sum * p_keep), LSE
     if (active) {

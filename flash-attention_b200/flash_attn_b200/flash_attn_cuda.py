@@ -19,7 +19,7 @@ def _status_buffer(device):
     """Per-device int32[4] the kernels write to when they abandon a bounded wait."""
     buf = _status.get(device)
     if buf is None:
-        buf = torch.zeros(4, dtype=torch.int32, device=device)
+        buf = torch.zeros(64, dtype=torch.int32, device=device)
         _status[device] = buf
     return buf
 
@@ -30,7 +30,7 @@ def check_device_status(device=None):
     buf = _status.get(device)
     if buf is None:
         return
-    val = buf.cpu().tolist()
+    val = buf[:4].cpu().tolist()
     if any(val):
         buf.zero_()
         raise RuntimeError("fa_b200: a kernel abandoned a bounded wait (status %s)" % val)
