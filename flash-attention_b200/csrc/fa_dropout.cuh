@@ -29,9 +29,19 @@ struct DropoutParams {
   int32_t head_offset;
 };
 
+__host__ __device__ __forceinline__ uint64_t mul_wide_u32(uint32_t a, uint32_t b) {
+#ifdef __CUDA_ARCH__
+  uint64_t r;
+  asm("mul.wide.u32 %0, %1, %2;" : "=l"(r) : "r"(a), "r"(b));
+  return r;
+#else
+  return static_cast<uint64_t>(a) * b;
+#endif
+}
+
 __host__ __device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
-  const uint64_t p0 = static_cast<uint64_t>(0xD2511F53u) * c[0];
-  const uint64_t p1 = static_cast<uint64_t>(0xCD9E8D57u) * c[2];
+  const uint64_t p0 = mul_wide_u32(0xD2511F53u, c[0]);
+  const uint64_t p1 = mul_wide_u32(0xCD9E8D57u, c[2]);
   const uint32_t n0 = static_cast<uint32_t>(p1 >> 32) ^ c[1] ^ k0;
   const uint32_t n1 = static_cast<uint32_t>(p1);
   const uint32_t n2 = static_cast<uint32_t>(p0 >> 32) ^ c[3] ^ k1;
@@ -132,6 +142,22 @@ __host__ __device__ __forceinline__ void fa_philox_call(const DropoutParams& dp,
   c[3] = static_cast<uint32_t>(subseq >> 32);
 #pragma unroll
   for (int r = 0; r < 7; ++r) philox_round(c, pk.k0[r], pk.k1[r]);
+}
+
+// Counter words of that call without running the rounds (for callers that interleave the rounds
+// of many independent calls).
+__host__ __device__ __forceinline__ void fa_philox_init(const DropoutParams& dp, int64_t bh_sub, int32_t i,
+                                                        int32_t jg0, int32_t q, int64_t iter_index,
+                                                        uint32_t (&c)[4]) {
+  const int32_t n_mask = (1 << dp.n_shift) - 1;
+  const int32_t c16 = (jg0 & n_mask) >> 4;
+  const uint64_t subseq = static_cast<uint64_t>(bh_sub) + (c16 & 7) * 32 + (i & 7) * 4 + q;
+  const uint64_t ctr = dp.counter_base + static_cast<uint64_t>(iter_index << (dp.n_shift - 7)) +
+                       static_cast<uint64_t>(c16 >> 3);
+  c[0] = static_cast<uint32_t>(ctr);
+  c[1] = static_cast<uint32_t>(ctr >> 32);
+  c[2] = static_cast<uint32_t>(subseq);
+  c[3] = static_cast<uint32_t>(subseq >> 32);
 }
 
 }  // namespace fa

@@ -457,16 +457,27 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
       FA_PROF(5)
       if constexpr (DROPOUT) {
+        // 16 independent Philox calls (8 column groups x 2 quarters), rounds interleaved so the
+        // multiply chains of different calls overlap.
+        uint32_t st[16][4];
+        const int q0 = hi_lane ? 2 : 0;
 #pragma unroll
         for (int grp = 0; grp < 8; ++grp) {
           const int jg0 = col0 + grp * 16;
           int64_t it_index;
           if constexpr (BLOCKSPARSE) it_index = bs_it;
           else it_index = fa_iter_index(CAUSAL, jg0 >> a.drop.n_shift, ig >> 4, L16, a.drop.n_shift);
-          uint32_t ca[4], cb[4];
-          const int q0 = hi_lane ? 2 : 0;
-          fa_philox_call(a.drop, keys, bh_sub, ig, jg0, q0, it_index, ca);
-          fa_philox_call(a.drop, keys, bh_sub, ig, jg0, q0 + 1, it_index, cb);
+          fa_philox_init(a.drop, bh_sub, ig, jg0, q0, it_index, st[2 * grp]);
+          fa_philox_init(a.drop, bh_sub, ig, jg0, q0 + 1, it_index, st[2 * grp + 1]);
+        }
+#pragma unroll
+        for (int r = 0; r < 7; ++r)
+#pragma unroll
+          for (int k = 0; k < 16; ++k) philox_round(st[k], keys.k0[r], keys.k1[r]);
+#pragma unroll
+        for (int grp = 0; grp < 8; ++grp) {
+          const uint32_t(&ca)[4] = st[2 * grp];
+          const uint32_t(&cb)[4] = st[2 * grp + 1];
           // words this row keeps from its own calls / words it hands to the partner row
           const uint32_t ka0 = hi_lane ? ca[2] : ca[0], ka1 = hi_lane ? ca[3] : ca[1];
           const uint32_t kb0 = hi_lane ? cb[2] : cb[0], kb1 = hi_lane ? cb[3] : cb[1];
