@@ -17,13 +17,17 @@
 // (:333), dropped entries contribute -P*D (:402-418), dQ and dK scaled by scale/p_keep (:583,
 // :628), dV by 1/p_keep (:613-619), P~ and dS rounded to the 16-bit type before their products.
 //
-// Warp roles in bwd_main (384 threads):
-//   warps 0-3   compute group: S, dP -> P~, dS (one thread per query row), dV epilogue
-//   warps 4-7   dQ group: tensor memory -> global reductions, dK epilogue
-//   warp  8     TMA producer          warp 9   tcgen05.mma issuer          warps 10-11 idle
+// Warp roles in bwd_main (512 threads):
+//   warps 0-3   compute group 0: key columns 0-63 of the tile, S, dP -> P~, dS (one thread per
+//               query row); dV epilogue
+//   warps 4-7   compute group 1: key columns 64-127; dK epilogue
+//   warps 8-11  dQ group: tensor memory -> global reductions
+//   warp 12     TMA producer     warp 13  MMA issuer (S, dP, dQ; everything at d = 128)
+//   warp 14     second MMA issuer (dV, dK) at d = 64      warp 15 idle
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "fa_kernels.h"
+#include "fa_math.cuh"
 #include "sm100_prims.cuh"
 
 namespace fa {
@@ -32,13 +36,14 @@ namespace {
 
 constexpr int kBM = 128;  // query rows per tile
 constexpr int kBN = 128;  // key rows per tile
-constexpr int kBwdThreads = 384;
+constexpr int kBwdThreads = 512;
 constexpr int kMaxSparseTiles = 1024;  // query tiles of 128 per sequence in block-sparse mode
 
 template <int D>
 struct BwdCfg {
   static constexpr int kQStages = (D == 64) ? 2 : 1;
   static constexpr bool kAliasDq = (D == 128);  // dQ shares tensor-memory columns with dP
+  static constexpr bool kDualIssue = (D == 64);  // second MMA-issuing warp for dV, dK
   static constexpr int kTileBytes = 128 * D * 2;
   static constexpr int kPdsBytes = 128 * 128 * 2;
   // K, V, (Q, dO) x stages, P~, dS
@@ -181,14 +186,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       mbar_init(smem_u32(&sh.q_empty[i]), 1);
     }
     mbar_init(smem_u32(&sh.sdp_full), 1);
-    mbar_init(smem_u32(&sh.sdp_consumed), kBM);
-    mbar_init(smem_u32(&sh.pds_ready), kBM);
-    mbar_init(smem_u32(&sh.pds_free), 1);
+    mbar_init(smem_u32(&sh.sdp_consumed), 2 * kBM);
+    mbar_init(smem_u32(&sh.pds_ready), 2 * kBM);
+    mbar_init(smem_u32(&sh.pds_free), Cfg::kDualIssue ? 2 : 1);
     mbar_init(smem_u32(&sh.dq_full), 1);
     mbar_init(smem_u32(&sh.dq_consumed), kBM);
     fence_mbar_init();
   }
-  if (warp == 8) tmem_alloc(smem_u32(&sh.tmem_base), 512);
+  if (warp == 12) tmem_alloc(smem_u32(&sh.tmem_base), 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -197,9 +202,41 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
   const float rp_keep = ka.rp_keep;
 
-  if (warp >= 8) {
-    reg_dealloc<40>();
-    if (warp == 8 && lane == 0) {
+  // operand descriptors of the five products
+  constexpr uint32_t idesc_s = make_idesc(BF16, false, false, 128, 128);   // Q K^T, dO V^T
+  constexpr uint32_t idesc_tt = make_idesc(BF16, true, true, 128, D);      // P~^T dO, dS^T Q
+  constexpr uint32_t idesc_dq = make_idesc(BF16, false, true, 128, D);     // dS K
+  auto issue_kk = [&](uint32_t dst, uint32_t a_base, uint32_t b_base) {  // both K-major, K = D
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+      mma_ss(dst, make_smem_desc(a_base + off, 16, 1024), make_smem_desc(b_base + off, 16, 1024),
+             idesc_s, ks > 0);
+    }
+  };
+  auto issue_tt = [&](uint32_t dst, uint32_t a_base, uint32_t b_base, bool acc) {
+    // A = [q][kv] read as M = kv (MN-major); B = [q][d] read as N = d (MN-major); K = q rows
+#pragma unroll
+    for (int ks = 0; ks < kBM / 16; ++ks) {
+      mma_ss(dst, make_smem_desc(a_base + ks * 2048, 16384, 1024),
+             make_smem_desc(b_base + ks * 2048, 16384, 1024), idesc_tt, acc || ks > 0);
+    }
+  };
+  auto issue_dq = [&](uint32_t dst, uint32_t a_base, uint32_t b_base) {
+    // A = dS [q][kv] K-major; B = K [kv][d] read as N = d (MN-major); K = kv
+#pragma unroll
+    for (int ks = 0; ks < kBN / 16; ++ks) {
+      const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+      mma_ss(dst, make_smem_desc(a_base + off, 16, 1024),
+             make_smem_desc(b_base + ks * 2048, 16384, 1024), idesc_dq, ks > 0);
+    }
+  };
+  const uint32_t tS_ = tmem + Cfg::kTmemS, tDP_ = tmem + Cfg::kTmemDP;
+  const uint32_t tDV_ = tmem + Cfg::kTmemDV, tDK_ = tmem + Cfg::kTmemDK, tDQ_ = tmem + Cfg::kTmemDQ;
+
+  if (warp >= 12) {
+    reg_dealloc<56>();
+    if (warp == 12 && lane == 0) {
       // -------------------------------------------------------------- TMA producer
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
@@ -227,46 +264,15 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           tma_load_3d(smem_do + s * Cfg::kTileBytes + p * 16384, &tm_do, bar, p * 64, row, h);
         }
       }
-    } else if (warp == 9 && lane == 0) {
-      // -------------------------------------------------------------- MMA issuer
-      constexpr uint32_t idesc_s = make_idesc(BF16, false, false, 128, 128);   // Q K^T, dO V^T
-      constexpr uint32_t idesc_tt = make_idesc(BF16, true, true, 128, D);      // P~^T dO, dS^T Q
-      constexpr uint32_t idesc_dq = make_idesc(BF16, false, true, 128, D);     // dS K
-      const uint32_t tS = tmem + Cfg::kTmemS, tDP = tmem + Cfg::kTmemDP;
-      const uint32_t tDV = tmem + Cfg::kTmemDV, tDK = tmem + Cfg::kTmemDK, tDQ = tmem + Cfg::kTmemDQ;
-
-      auto issue_kk = [&](uint32_t dst, uint32_t a_base, uint32_t b_base) {  // both K-major, K = D
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-          mma_ss(dst, make_smem_desc(a_base + off, 16, 1024), make_smem_desc(b_base + off, 16, 1024),
-                 idesc_s, ks > 0);
-        }
-      };
-      auto issue_tt = [&](uint32_t dst, uint32_t a_base, uint32_t b_base, bool acc) {
-        // A = [q][kv] read as M = kv (MN-major); B = [q][d] read as N = d (MN-major); K = q rows
-#pragma unroll
-        for (int ks = 0; ks < kBM / 16; ++ks) {
-          mma_ss(dst, make_smem_desc(a_base + ks * 2048, 16384, 1024),
-                 make_smem_desc(b_base + ks * 2048, 16384, 1024), idesc_tt, acc || ks > 0);
-        }
-      };
-      auto issue_dq = [&](uint32_t dst, uint32_t a_base, uint32_t b_base) {
-        // A = dS [q][kv] K-major; B = K [kv][d] read as N = d (MN-major); K = kv
-#pragma unroll
-        for (int ks = 0; ks < kBN / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-          mma_ss(dst, make_smem_desc(a_base + off, 16, 1024),
-                 make_smem_desc(b_base + ks * 2048, 16384, 1024), idesc_dq, ks > 0);
-        }
-      };
-
+    } else if (warp == 13 && lane == 0) {
+      // -------------------------------------------------------------- MMA issuer 1
+      // d = 64: S, dP and dQ (dV, dK go through issuer 2).  d = 128: every product, in order.
       bool ok = mbar_wait(smem_u32(&sh.kv_full), 0, abort_flag);
       if (ok) ok = mbar_wait(smem_u32(&sh.q_full[0]), 0, abort_flag);
       if (ok) {
         tc_fence_after();
-        issue_kk(tS, smem_q, smem_k);
-        issue_kk(tDP, smem_do, smem_v);
+        issue_kk(tS_, smem_q, smem_k);
+        issue_kk(tDP_, smem_do, smem_v);
         mma_commit(smem_u32(&sh.sdp_full));
       }
       for (int t = 0; t < nm && ok; ++t) {
@@ -278,51 +284,75 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (ok) ok = mbar_wait(smem_u32(&sh.sdp_consumed), t & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          issue_kk(tS, smem_q + sn * Cfg::kTileBytes, smem_k);
-          issue_kk(tDP, smem_do + sn * Cfg::kTileBytes, smem_v);
+          issue_kk(tS_, smem_q + sn * Cfg::kTileBytes, smem_k);
+          issue_kk(tDP_, smem_do + sn * Cfg::kTileBytes, smem_v);
           mma_commit(smem_u32(&sh.sdp_full));
         }
         ok = mbar_wait(smem_u32(&sh.pds_ready), t & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        issue_tt(tDV, smem_p, smem_do + s * Cfg::kTileBytes, t > 0);
-        issue_tt(tDK, smem_ds, smem_q + s * Cfg::kTileBytes, t > 0);
+        if (!Cfg::kDualIssue) {
+          issue_tt(tDV_, smem_p, smem_do + s * Cfg::kTileBytes, t > 0);
+          issue_tt(tDK_, smem_ds, smem_q + s * Cfg::kTileBytes, t > 0);
+        }
         if (!Cfg::kAliasDq && t > 0) {
           ok = mbar_wait(smem_u32(&sh.dq_consumed), (t - 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
         }
-        issue_dq(tDQ, smem_ds, smem_k);
+        issue_dq(tDQ_, smem_ds, smem_k);
         mma_commit(smem_u32(&sh.dq_full));
         mma_commit(smem_u32(&sh.pds_free));
-        mma_commit(smem_u32(&sh.q_empty[s]));
+        if (!Cfg::kDualIssue) mma_commit(smem_u32(&sh.q_empty[s]));
         if (Cfg::kQStages == 1 && has_next) {
           ok = mbar_wait(smem_u32(&sh.q_full[0]), (t + 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          issue_kk(tS, smem_q, smem_k);
+          issue_kk(tS_, smem_q, smem_k);
           if (Cfg::kAliasDq) {
             ok = mbar_wait(smem_u32(&sh.dq_consumed), t & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
           }
-          issue_kk(tDP, smem_do, smem_v);
+          issue_kk(tDP_, smem_do, smem_v);
           mma_commit(smem_u32(&sh.sdp_full));
         }
       }
+    } else if (warp == 14 && lane == 0 && Cfg::kDualIssue) {
+      // -------------------------------------------------------------- MMA issuer 2: dV, dK
+      bool ok = true;
+      for (int t = 0; t < nm && ok; ++t) {
+        const int s = t % Cfg::kQStages;
+        ok = mbar_wait(smem_u32(&sh.pds_ready), t & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        issue_tt(tDV_, smem_p, smem_do + s * Cfg::kTileBytes, t > 0);
+        issue_tt(tDK_, smem_ds, smem_q + s * Cfg::kTileBytes, t > 0);
+        mma_commit(smem_u32(&sh.pds_free));
+        mma_commit(smem_u32(&sh.q_empty[s]));
+      }
     }
-  } else if (warp < 4) {
-    // ------------------------------------------------------------------ compute group
-    reg_alloc<240>();
-    const int row = tid;  // 0..127
-    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t tS = tmem + Cfg::kTmemS + lane_sel;
-    const uint32_t tDP = tmem + Cfg::kTmemDP + lane_sel;
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ compute groups
+    // group w (0 / 1) owns key columns [64 w, 64 w + 64) of the tile; one thread per query row
+    reg_alloc<184>();
+    const int w = warp >> 2;
+    const int row = tid & 127;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tS_ + lane_sel + w * 64;
+    const uint32_t tDP = tDP_ + lane_sel + w * 64;
     const int64_t bh_sub =
         (static_cast<int64_t>(b) * ka.drop.heads_total + ka.drop.head_offset + h) * 256;
     const int L16 = (sq + 15) >> 4;
     const float* lse_row = ka.lse + (static_cast<int64_t>(b) * ka.heads + h) * ka.lse_stride;
     const float* d_row = a.softmax_d + (static_cast<int64_t>(b) * ka.heads + h) * ka.lse_stride;
+    const uint64_t c2 = pack_f2(ka.scale_log2, ka.scale_log2);
+    const bool hi_lane = (row & 8) != 0;
+    const uint32_t thr = ka.drop.threshold;
+    const uint32_t thr_hi = (thr + 1u) << 16;
+    PhiloxKeys keys;
+    if constexpr (DROPOUT) keys.init(ka.drop.key0, ka.drop.key1);
+    const int cbase = n0 + w * 64;  // first key column of this thread
     bool ok = true;
 
     for (int t = 0; t < nm && ok; ++t) {
@@ -331,6 +361,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const bool row_valid = ig < sq;
       const float lse2 = row_valid ? lse_row[ig] * 1.4426950408889634f : INFINITY;
       const float d_i = row_valid ? d_row[ig] : 0.f;
+      const uint64_t nlse2 = pack_f2(-lse2, -lse2);
+      const uint64_t nd2 = pack_f2(-d_i, -d_i);
       bool row_in_layout = true;
       int32_t bs_it = 0;
       if constexpr (BLOCKSPARSE) {
@@ -345,46 +377,81 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (!ok) break;
       tc_fence_after();
 
-      uint32_t pp[64], pds[64];
+      uint32_t pp[32], pds[32];
       const bool need_mask = (n0 + kBN > sk) || (CAUSAL && (n0 + kBN - 1 > m0));
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t sr[32], dr[32];
         tmem_ld32(tS + c * 32, sr);
         tmem_ld32(tDP + c * 32, dr);
-        tmem_wait_ld();
-        uint32_t keep = 0xffffffffu;
+
+        // keep words of the 16 column pairs of this chunk (two 16-column groups)
+        uint32_t wd[16];
         if constexpr (DROPOUT) {
-          keep = 0;
+          uint32_t st[4][4];
+          const int q0 = hi_lane ? 2 : 0;
 #pragma unroll
-          for (int hg = 0; hg < 2; ++hg) {
-            const int jg0 = n0 + c * 32 + hg * 16;
+          for (int g2 = 0; g2 < 2; ++g2) {
+            const int jg0 = cbase + c * 32 + g2 * 16;
             int64_t it;
             if constexpr (BLOCKSPARSE) it = bs_it;
             else it = fa_iter_index(CAUSAL, jg0 >> ka.drop.n_shift, ig >> 4, L16, ka.drop.n_shift);
-            keep |= fa_dropout_keep16(ka.drop, bh_sub, ig, jg0, it) << (hg * 16);
+            fa_philox_init(ka.drop, bh_sub, ig, jg0, q0, it, st[2 * g2]);
+            fa_philox_init(ka.drop, bh_sub, ig, jg0, q0 + 1, it, st[2 * g2 + 1]);
+          }
+#pragma unroll
+          for (int r = 0; r < 7; ++r)
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) philox_round(st[k4], keys.k0[r], keys.k1[r]);
+#pragma unroll
+          for (int g2 = 0; g2 < 2; ++g2) {
+            const uint32_t(&ca)[4] = st[2 * g2];
+            const uint32_t(&cb)[4] = st[2 * g2 + 1];
+            const uint32_t ka0 = hi_lane ? ca[2] : ca[0], ka1 = hi_lane ? ca[3] : ca[1];
+            const uint32_t kb0 = hi_lane ? cb[2] : cb[0], kb1 = hi_lane ? cb[3] : cb[1];
+            const uint32_t ra0 = __shfl_xor_sync(0xffffffffu, hi_lane ? ca[0] : ca[2], 8);
+            const uint32_t ra1 = __shfl_xor_sync(0xffffffffu, hi_lane ? ca[1] : ca[3], 8);
+            const uint32_t rb0 = __shfl_xor_sync(0xffffffffu, hi_lane ? cb[0] : cb[2], 8);
+            const uint32_t rb1 = __shfl_xor_sync(0xffffffffu, hi_lane ? cb[1] : cb[3], 8);
+            uint32_t* wg = wd + g2 * 8;
+            wg[0] = hi_lane ? ra0 : ka0; wg[4] = hi_lane ? ra1 : ka1;
+            wg[1] = hi_lane ? rb0 : kb0; wg[5] = hi_lane ? rb1 : kb1;
+            wg[2] = hi_lane ? ka0 : ra0; wg[6] = hi_lane ? ka1 : ra1;
+            wg[3] = hi_lane ? kb0 : rb0; wg[7] = hi_lane ? kb1 : rb1;
           }
         }
-        float pv[32], dsv[32];
+        tmem_wait_ld();
+
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float p = ex2(fmaf(__uint_as_float(sr[i]), ka.scale_log2, -lse2));
+        for (int i = 0; i < 32; i += 2) {
+          float p0, p1;
+          unpack_f2(fma2(pack_f2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), c2, nlse2), p0, p1);
+          p0 = ex2f(p0);
+          p1 = ex2f(p1);
           if (need_mask) {
-            const int col = n0 + c * 32 + i;
-            bool valid = col < sk;
-            if (CAUSAL) valid = valid && (col <= ig);
-            if (!valid) p = 0.f;
+            const int col = cbase + c * 32 + i;
+            bool v0 = col < sk, v1 = col + 1 < sk;
+            if (CAUSAL) { v0 = v0 && (col <= ig); v1 = v1 && (col + 1 <= ig); }
+            if (!v0) p0 = 0.f;
+            if (!v1) p1 = 0.f;
           }
-          if (BLOCKSPARSE && !row_in_layout) p = 0.f;
-          const float dp = __uint_as_float(dr[i]);
-          const bool kept = (keep >> i) & 1u;
-          pv[i] = kept ? p : 0.f;
-          dsv[i] = kept ? p * (dp - d_i) : -p * d_i;
-        }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          pp[c * 16 + i] = pack16<BF16>(pv[2 * i], pv[2 * i + 1]);
-          pds[c * 16 + i] = pack16<BF16>(dsv[2 * i], dsv[2 * i + 1]);
+          if (BLOCKSPARSE && !row_in_layout) { p0 = 0.f; p1 = 0.f; }
+          float g0 = __uint_as_float(dr[i]), g1 = __uint_as_float(dr[i + 1]);
+          float k0 = p0, k1 = p1;
+          if constexpr (DROPOUT) {
+            const uint32_t word = wd[i >> 1];
+            const bool keep0 = (word & 0xffffu) <= thr;
+            const bool keep1 = word < thr_hi;
+            g0 = keep0 ? g0 : 0.f;
+            g1 = keep1 ? g1 : 0.f;
+            k0 = keep0 ? p0 : 0.f;
+            k1 = keep1 ? p1 : 0.f;
+          }
+          // dS = P * (keep * dP - D)
+          float s0, s1;
+          unpack_f2(mul2(pack_f2(p0, p1), add2(pack_f2(g0, g1), nd2)), s0, s1);
+          pp[c * 16 + (i >> 1)] = pack_lowp<BF16>(k0, k1);
+          pds[c * 16 + (i >> 1)] = pack_lowp<BF16>(s0, s1);
         }
       }
       tc_fence_before();
@@ -395,10 +462,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
-      // 128 16-bit values per row = 16 chunks of 16 bytes, two 64-column panels
+      // 64 16-bit values per row = 8 chunks of 16 bytes in the 64-column panel w
 #pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {
-        const uint32_t off = (ch >> 3) * 16384 + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
+      for (int ch = 0; ch < 8; ++ch) {
+        const uint32_t off = w * 16384 + row * 128 + ((ch ^ (row & 7)) << 4);
         *reinterpret_cast<uint4*>(p_ptr + off) =
             make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
         *reinterpret_cast<uint4*>(ds_ptr + off) =
@@ -408,27 +475,29 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       mbar_arrive(smem_u32(&sh.pds_ready));
     }
 
-    // ---------------- epilogue: dV = acc / p_keep
+    // ---------------- epilogue: group 0 writes dV = acc / p_keep, group 1 writes dK = acc * scale / p_keep
     if (ok) {
       ok = mbar_wait(smem_u32(&sh.pds_free), (nm - 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
       tc_fence_after();
-      const uint32_t tDV = tmem + Cfg::kTmemDV + lane_sel;
+      const uint32_t tAcc = (w == 0 ? tDV_ : tDK_) + lane_sel;
+      const float f = (w == 0) ? rp_keep : ka.scale * rp_keep;
       const int kr = n0 + row;
-      uint16_t* dst_row = dv_base + static_cast<int64_t>(k_start + kr) * a.dv_row_stride +
-                          static_cast<int64_t>(h) * a.dv_head_stride;
+      uint16_t* dst_row = (w == 0)
+          ? dv_base + static_cast<int64_t>(k_start + kr) * a.dv_row_stride + static_cast<int64_t>(h) * a.dv_head_stride
+          : dk_base + static_cast<int64_t>(k_start + kr) * a.dk_row_stride + static_cast<int64_t>(h) * a.dk_head_stride;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
-        tmem_ld32(tDV + c * 32, r);
+        tmem_ld32(tAcc + c * 32, r);
         tmem_wait_ld();
         if (kr < sk && c * 32 < ka.head_dim) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            pk[i] = pack16<BF16>(__uint_as_float(r[2 * i]) * rp_keep, __uint_as_float(r[2 * i + 1]) * rp_keep);
+            pk[i] = pack_lowp<BF16>(__uint_as_float(r[2 * i]) * f, __uint_as_float(r[2 * i + 1]) * f);
           uint4* dst = reinterpret_cast<uint4*>(dst_row + c * 32);
           const int nvec = min(4, (ka.head_dim - c * 32) / 8);
 #pragma unroll
@@ -438,11 +507,11 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
     }
   } else {
-    // ------------------------------------------------------------------ dQ group (warps 4-7)
-    reg_dealloc<104>();
-    const int row = tid - 128;
+    // ------------------------------------------------------------------ dQ group (warps 8-11)
+    reg_dealloc<88>();
+    const int row = tid - 256;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tDQ = tmem + Cfg::kTmemDQ + lane_sel;
+    const uint32_t tDQ = tDQ_ + lane_sel;
     bool ok = true;
     for (int t = 0; t < nm && ok; ++t) {
       const int ig = q_tile(t) * kBM + row;
@@ -466,37 +535,11 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       tc_fence_before();
       mbar_arrive(smem_u32(&sh.dq_consumed));
     }
-    // ---------------- epilogue: dK = acc * scale / p_keep
-    if (ok) {
-      tc_fence_after();
-      const uint32_t tDK = tmem + Cfg::kTmemDK + lane_sel;
-      const int kr = n0 + row;
-      const float f = ka.scale * rp_keep;
-      uint16_t* dst_row = dk_base + static_cast<int64_t>(k_start + kr) * a.dk_row_stride +
-                          static_cast<int64_t>(h) * a.dk_head_stride;
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tDK + c * 32, r);
-        tmem_wait_ld();
-        if (kr < sk && c * 32 < ka.head_dim) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i)
-            pk[i] = pack16<BF16>(__uint_as_float(r[2 * i]) * f, __uint_as_float(r[2 * i + 1]) * f);
-          uint4* dst = reinterpret_cast<uint4*>(dst_row + c * 32);
-          const int nvec = min(4, (ka.head_dim - c * 32) / 8);
-#pragma unroll
-          for (int v = 0; v < 4; ++v)
-            if (v < nvec) dst[v] = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
-        }
-      }
-    }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == 12) {
     tmem_dealloc(tmem, 512);
     if (lane == 0 && sh.abort_flag && ka.status) atomicExch(ka.status + 1, 1);
   }
