@@ -77,6 +77,23 @@ int make_tile_map(CUtensorMap* tm, const void* base, bool bf16, int64_t rows, in
   return FA_OK;
 }
 
+// fp32 dQ accumulator [rows, heads, dpad]: box = 32 columns x 128 rows x 1 head, 128-byte swizzle
+// (the layout the backward kernel stages dQ tiles in before its TMA reduce-add).
+int make_accum_map(CUtensorMap* tm, float* base, int64_t rows, int heads, int dpad) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(dpad), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(heads)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(heads) * dpad * 4, static_cast<cuuint64_t>(dpad) * 4};
+  cuuint32_t box[3] = {32, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled (accumulator) failed with code " + std::to_string((int)r));
+  return FA_OK;
+}
+
 int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
 int validate_common(const fa_fwd_params* p) {
@@ -302,6 +319,7 @@ int fa_bwd(const fa_bwd_params* p, void* cuda_stream) {
                              f->v_row_stride, f->v_head_stride, 128)) return rc;
   if (int rc = make_tile_map(&l.tm_do, p->dout, l.is_bf16, f->total_q, f->heads, f->head_dim,
                              a.do_row_stride, a.do_head_stride, 128)) return rc;
+  if (int rc = make_accum_map(&l.tm_dq, a.dq_accum, f->total_q, f->heads, l.dpad)) return rc;
   FA_CUDA(fa::launch_bwd(l, static_cast<cudaStream_t>(cuda_stream)));
   return FA_OK;
 }
@@ -423,6 +441,7 @@ int fa_bwd_static_scratch(const fa_bwd_params* p, void* cuda_stream) {
                                f->v_row_stride, f->v_head_stride)) return rc;
   if (int rc = encode_tile_map(&l.tm_do, p->dout, l.is_bf16, f->total_q, f->heads, f->head_dim,
                                a.do_row_stride, a.do_head_stride)) return rc;
+  if (int rc = make_accum_map(&l.tm_dq, a.dq_accum, f->total_q, f->heads, l.dpad)) return rc;
   FA_CUDA(fa::launch_bwd(l, static_cast<cudaStream_t>(cuda_stream)));
   return FA_OK;
 }

@@ -46,8 +46,9 @@ struct BwdCfg {
   static constexpr bool kDualIssue = (D == 64);  // second MMA-issuing warp for dV, dK
   static constexpr int kTileBytes = 128 * D * 2;
   static constexpr int kPdsBytes = 128 * 128 * 2;
-  // K, V, (Q, dO) x stages, P~, dS
-  static constexpr int kSmemBytes = (2 + 2 * kQStages) * kTileBytes + 2 * kPdsBytes + 1024;
+  static constexpr int kDqStageBytes = 2 * 16384;  // two [128 rows x 32 fp32] boxes
+  // K, V, (Q, dO) x stages, P~, dS, dQ staging
+  static constexpr int kSmemBytes = (2 + 2 * kQStages) * kTileBytes + 2 * kPdsBytes + kDqStageBytes + 1024;
   static constexpr uint32_t kTmemS = 0, kTmemDP = 128, kTmemDV = 256, kTmemDK = 256 + D;
   static constexpr uint32_t kTmemDQ = kAliasDq ? 128 : 256 + 2 * D;
 };
@@ -56,6 +57,7 @@ struct BwdShared {
   uint64_t kv_full;
   uint64_t q_full[2], q_empty[2];
   uint64_t sdp_full, sdp_consumed, pds_ready, pds_free, dq_full, dq_consumed;
+  uint64_t dq_group;  // rendezvous of the 128 threads of the dQ group (bounded, unlike bar.sync)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -83,6 +85,19 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
+// Optional cycle accounting (build with -DFA_PROFILE): one thread of each role of CTA (0,0,0)
+// accumulates the cycles it spends per phase into status[8..].
+#ifdef FA_PROFILE
+#define FA_PROF_DECL long long prof_t = clock64(); long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define FA_PROF(slot) { const long long now_ = clock64(); prof_acc[slot] += now_ - prof_t; prof_t = now_; }
+#define FA_PROF_FLUSH(base, n) if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && ka.status) { \
+    for (int i_ = 0; i_ < 8; ++i_) ka.status[(base) + i_] = static_cast<int32_t>(prof_acc[i_] / ((n) > 0 ? (n) : 1)); }
+#else
+#define FA_PROF_DECL
+#define FA_PROF(slot)
+#define FA_PROF_FLUSH(base, n)
+#endif
+
 template <int N>
 __device__ __forceinline__ void reg_alloc() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
@@ -97,7 +112,7 @@ template <int D, bool BF16, bool CAUSAL, bool DROPOUT, bool BLOCKSPARSE>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-              const BwdArgs a) {
+              const __grid_constant__ CUtensorMap tm_dq, const BwdArgs a) {
   using Cfg = BwdCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ BwdShared sh;
@@ -177,6 +192,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const uint32_t smem_ds = smem_p + Cfg::kPdsBytes;
   uint8_t* p_ptr = smem + (2 + 2 * Cfg::kQStages) * Cfg::kTileBytes;
   uint8_t* ds_ptr = p_ptr + Cfg::kPdsBytes;
+  uint8_t* dq_stage = ds_ptr + Cfg::kPdsBytes;
 
   if (tid == 0) {
     sh.abort_flag = 0;
@@ -191,6 +207,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     mbar_init(smem_u32(&sh.pds_free), Cfg::kDualIssue ? 2 : 1);
     mbar_init(smem_u32(&sh.dq_full), 1);
     mbar_init(smem_u32(&sh.dq_consumed), kBM);
+    mbar_init(smem_u32(&sh.dq_group), kBM);
     fence_mbar_init();
   }
   if (warp == 12) tmem_alloc(smem_u32(&sh.tmem_base), 512);
@@ -235,13 +252,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const uint32_t tDV_ = tmem + Cfg::kTmemDV, tDK_ = tmem + Cfg::kTmemDK, tDQ_ = tmem + Cfg::kTmemDQ;
 
   if (warp >= 12) {
-    reg_dealloc<56>();
+    reg_dealloc<72>();
     if (warp == 12 && lane == 0) {
       // -------------------------------------------------------------- TMA producer
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
       tma_prefetch_desc(&tm_do);
+      tma_prefetch_desc(&tm_dq);
       {
         const uint32_t bar = smem_u32(&sh.kv_full);
         mbar_expect_tx(bar, 2 * Cfg::kTileBytes);
@@ -275,21 +293,26 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         issue_kk(tDP_, smem_do, smem_v);
         mma_commit(smem_u32(&sh.sdp_full));
       }
+      FA_PROF_DECL
       for (int t = 0; t < nm && ok; ++t) {
         const int s = t % Cfg::kQStages;
         const bool has_next = t + 1 < nm;
         const int sn = (t + 1) % Cfg::kQStages;
+        FA_PROF(0)
         if (Cfg::kQStages > 1 && has_next) {
           ok = mbar_wait(smem_u32(&sh.q_full[sn]), ((t + 1) / Cfg::kQStages) & 1, abort_flag);
           if (ok) ok = mbar_wait(smem_u32(&sh.sdp_consumed), t & 1, abort_flag);
           if (!ok) break;
+          FA_PROF(1)
           tc_fence_after();
           issue_kk(tS_, smem_q + sn * Cfg::kTileBytes, smem_k);
           issue_kk(tDP_, smem_do + sn * Cfg::kTileBytes, smem_v);
           mma_commit(smem_u32(&sh.sdp_full));
+          FA_PROF(2)
         }
         ok = mbar_wait(smem_u32(&sh.pds_ready), t & 1, abort_flag);
         if (!ok) break;
+        FA_PROF(3)
         tc_fence_after();
         if (!Cfg::kDualIssue) {
           issue_tt(tDV_, smem_p, smem_do + s * Cfg::kTileBytes, t > 0);
@@ -300,10 +323,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (!ok) break;
           tc_fence_after();
         }
+        FA_PROF(4)
         issue_dq(tDQ_, smem_ds, smem_k);
         mma_commit(smem_u32(&sh.dq_full));
         mma_commit(smem_u32(&sh.pds_free));
         if (!Cfg::kDualIssue) mma_commit(smem_u32(&sh.q_empty[s]));
+        FA_PROF(5)
         if (Cfg::kQStages == 1 && has_next) {
           ok = mbar_wait(smem_u32(&sh.q_full[0]), (t + 1) & 1, abort_flag);
           if (!ok) break;
@@ -316,26 +341,33 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           }
           issue_kk(tDP_, smem_do, smem_v);
           mma_commit(smem_u32(&sh.sdp_full));
+          FA_PROF(6)
         }
       }
+      FA_PROF_FLUSH(16, nm)
     } else if (warp == 14 && lane == 0 && Cfg::kDualIssue) {
       // -------------------------------------------------------------- MMA issuer 2: dV, dK
       bool ok = true;
+      FA_PROF_DECL
       for (int t = 0; t < nm && ok; ++t) {
         const int s = t % Cfg::kQStages;
+        FA_PROF(0)
         ok = mbar_wait(smem_u32(&sh.pds_ready), t & 1, abort_flag);
         if (!ok) break;
+        FA_PROF(1)
         tc_fence_after();
         issue_tt(tDV_, smem_p, smem_do + s * Cfg::kTileBytes, t > 0);
         issue_tt(tDK_, smem_ds, smem_q + s * Cfg::kTileBytes, t > 0);
         mma_commit(smem_u32(&sh.pds_free));
         mma_commit(smem_u32(&sh.q_empty[s]));
+        FA_PROF(2)
       }
+      FA_PROF_FLUSH(24, nm)
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ compute groups
     // group w (0 / 1) owns key columns [64 w, 64 w + 64) of the tile; one thread per query row
-    reg_alloc<184>();
+    reg_alloc<176>();
     const int w = warp >> 2;
     const int row = tid & 127;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -354,27 +386,41 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     if constexpr (DROPOUT) keys.init(ka.drop.key0, ka.drop.key1);
     const int cbase = n0 + w * 64;  // first key column of this thread
     bool ok = true;
+    FA_PROF_DECL
+
+    // per-row statistics of the first tile; those of tile t + 1 are fetched while tile t is processed
+    float lse_next = INFINITY, d_next = 0.f;
+    int32_t bs_next = 0;
+    auto fetch_row_stats = [&](int t) {
+      const int ig_n = q_tile(t) * kBM + row;
+      const bool valid = ig_n < sq;
+      lse_next = valid ? lse_row[ig_n] * 1.4426950408889634f : INFINITY;
+      d_next = valid ? d_row[ig_n] : 0.f;
+      if constexpr (BLOCKSPARSE) {
+        bs_next = (ig_n >> 4) < ka.bs_rows16
+                      ? ka.bs_iter[(static_cast<int64_t>(b) * ka.bs_kblocks + (n0 >> 8)) * ka.bs_rows16 + (ig_n >> 4)]
+                      : -1;
+      }
+    };
+    fetch_row_stats(0);
 
     for (int t = 0; t < nm && ok; ++t) {
+      FA_PROF(0)
       const int m0 = q_tile(t) * kBM;
       const int ig = m0 + row;
-      const bool row_valid = ig < sq;
-      const float lse2 = row_valid ? lse_row[ig] * 1.4426950408889634f : INFINITY;
-      const float d_i = row_valid ? d_row[ig] : 0.f;
+      const float lse2 = lse_next;
+      const float d_i = d_next;
       const uint64_t nlse2 = pack_f2(-lse2, -lse2);
       const uint64_t nd2 = pack_f2(-d_i, -d_i);
-      bool row_in_layout = true;
-      int32_t bs_it = 0;
-      if constexpr (BLOCKSPARSE) {
-        bs_it = (ig >> 4) < ka.bs_rows16
-                    ? ka.bs_iter[(static_cast<int64_t>(b) * ka.bs_kblocks + (n0 >> 8)) * ka.bs_rows16 + (ig >> 4)]
-                    : -1;
-        row_in_layout = bs_it >= 0;
-      }
+      const int32_t bs_it = bs_next;
+      const bool row_in_layout = !BLOCKSPARSE || bs_it >= 0;
+      if (t + 1 < nm) fetch_row_stats(t + 1);
 
+      FA_PROF(1)
       ok = mbar_wait(smem_u32(&sh.sdp_full), t & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      FA_PROF(2)
       tc_fence_after();
 
       uint32_t pp[32], pds[32];
@@ -453,27 +499,32 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           pp[c * 16 + (i >> 1)] = pack_lowp<BF16>(k0, k1);
           pds[c * 16 + (i >> 1)] = pack_lowp<BF16>(s0, s1);
         }
+        // the previous tile's products must have finished reading the P~ / dS buffers
+        if (c == 0 && t > 0) {
+          ok = mbar_wait(smem_u32(&sh.pds_free), (t - 1) & 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+        }
+        // 32 16-bit values = 4 chunks of 16 bytes of this row in the 64-column panel w
+#pragma unroll
+        for (int ch4 = 0; ch4 < 4; ++ch4) {
+          const int ch = c * 4 + ch4;
+          const uint32_t off = w * 16384 + row * 128 + ((ch ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(p_ptr + off) =
+              make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
+          *reinterpret_cast<uint4*>(ds_ptr + off) =
+              make_uint4(pds[4 * ch], pds[4 * ch + 1], pds[4 * ch + 2], pds[4 * ch + 3]);
+        }
       }
+      if (!ok) break;
       tc_fence_before();
       mbar_arrive(smem_u32(&sh.sdp_consumed));
-
-      if (t > 0) {
-        ok = mbar_wait(smem_u32(&sh.pds_free), (t - 1) & 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-      }
-      // 64 16-bit values per row = 8 chunks of 16 bytes in the 64-column panel w
-#pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        const uint32_t off = w * 16384 + row * 128 + ((ch ^ (row & 7)) << 4);
-        *reinterpret_cast<uint4*>(p_ptr + off) =
-            make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
-        *reinterpret_cast<uint4*>(ds_ptr + off) =
-            make_uint4(pds[4 * ch], pds[4 * ch + 1], pds[4 * ch + 2], pds[4 * ch + 3]);
-      }
+      FA_PROF(3)
+      FA_PROF(4)
       fence_async_smem();
       mbar_arrive(smem_u32(&sh.pds_ready));
+      FA_PROF(5)
     }
+    if (w == 0 && row == 0) { FA_PROF_FLUSH(8, nm) }
 
     // ---------------- epilogue: group 0 writes dV = acc / p_keep, group 1 writes dK = acc * scale / p_keep
     if (ok) {
@@ -508,33 +559,68 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
   } else {
     // ------------------------------------------------------------------ dQ group (warps 8-11)
+    // dQ tile: tensor memory -> registers -> swizzled fp32 staging in shared memory -> one TMA
+    // reduce-add per [128 rows x 32 columns] box into the fp32 accumulator.  Rows past the end of
+    // the sequence hold exact zeros (their P is zero), rows past the tensor are clipped by TMA.
     reg_dealloc<88>();
     const int row = tid - 256;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tDQ = tDQ_ + lane_sel;
+    const uint32_t stage_addr = smem_u32(dq_stage);
     bool ok = true;
+    bool pending = false;  // thread `row == 0`: a reduce group of this CTA may still read the staging
+    uint32_t sync_phase = 0;
+    auto group_sync = [&]() -> bool {
+      mbar_arrive(smem_u32(&sh.dq_group));
+      const bool done = mbar_wait(smem_u32(&sh.dq_group), sync_phase & 1, abort_flag);
+      ++sync_phase;
+      return done;
+    };
+    FA_PROF_DECL
     for (int t = 0; t < nm && ok; ++t) {
-      const int ig = q_tile(t) * kBM + row;
+      const int m0 = q_tile(t) * kBM;
+      FA_PROF(0)
       ok = mbar_wait(smem_u32(&sh.dq_full), t & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      FA_PROF(1)
       tc_fence_after();
-      float* acc_row = a.dq_accum + (static_cast<int64_t>(q_start + ig) * ka.heads + h) * D;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tDQ + c * 32, r);
+      for (int half = 0; half < D / 64; ++half) {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tDQ + half * 64, r0);
+        tmem_ld32(tDQ + half * 64 + 32, r1);
         tmem_wait_ld();
-        if (ig < sq) {
+        if (half == D / 64 - 1) {
+          tc_fence_before();
+          mbar_arrive(smem_u32(&sh.dq_consumed));
+        }
+        // the staging buffer is free once the previous reduce has read it
+        if (row == 0 && pending) bulk_wait_read();
+        ok = group_sync();
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
 #pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            red_add_v4(acc_row + c * 32 + i, __uint_as_float(r[i]), __uint_as_float(r[i + 1]),
-                       __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+        for (int ch = 0; ch < 8; ++ch) {
+          const uint32_t off = row * 128 + ((ch ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(dq_stage + off) = make_uint4(r0[4 * ch], r0[4 * ch + 1], r0[4 * ch + 2], r0[4 * ch + 3]);
+          *reinterpret_cast<uint4*>(dq_stage + 16384 + off) = make_uint4(r1[4 * ch], r1[4 * ch + 1], r1[4 * ch + 2], r1[4 * ch + 3]);
+        }
+        fence_async_smem();
+        ok = group_sync();
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (row == 0) {
+          tma_reduce_add_3d(&tm_dq, stage_addr, half * 64, q_start + m0, h);
+          tma_reduce_add_3d(&tm_dq, stage_addr + 16384, half * 64 + 32, q_start + m0, h);
+          bulk_commit();
+          pending = true;
         }
       }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&sh.dq_consumed));
+      FA_PROF(2)
     }
+    if (row == 0 && pending) bulk_wait_all();
+    if (row == 0) { FA_PROF_FLUSH(32, nm) }
   }
 
   tc_fence_before();
@@ -621,7 +707,7 @@ cudaError_t launch_main(const BwdLaunch& l, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   dim3 grid((l.args.max_seqlen_k + kBN - 1) / kBN, l.args.k.heads, l.args.k.batch);
-  kernel<<<grid, kBwdThreads, smem, stream>>>(l.tm_q, l.tm_k, l.tm_v, l.tm_do, l.args);
+  kernel<<<grid, kBwdThreads, smem, stream>>>(l.tm_q, l.tm_k, l.tm_v, l.tm_do, l.tm_dq, l.args);
   return cudaGetLastError();
 }
 

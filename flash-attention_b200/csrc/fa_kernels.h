@@ -52,6 +52,7 @@ struct FwdLaunch {
 
 struct BwdLaunch {
   CUtensorMap tm_q, tm_k, tm_v, tm_do;
+  CUtensorMap tm_dq;  // fp32 dQ accumulator [total_q, heads, dpad], 32-column boxes
   BwdArgs args;
   bool is_bf16, is_causal, is_dropout;
   int32_t dpad;  // 64 or 128
