@@ -259,6 +259,15 @@ int fa_debug_dropout_mask(uint8_t* mask_out, int32_t batch_idx, int32_t head_idx
   return FA_OK;
 }
 
+int fa_debug_philox(uint32_t* out, int32_t n, uint64_t seed, uint64_t offset, int32_t rounds,
+                    int32_t use_curand, void* cuda_stream) {
+  FA_REQUIRE(out != nullptr && n >= 0, "bad arguments");
+  FA_REQUIRE(use_curand || (rounds >= 1 && rounds <= 16), "rounds must be in [1, 16]");
+  FA_CUDA(fa::launch_philox_probe(out, n, seed, offset, rounds, use_curand ? 1 : 0,
+                                  static_cast<cudaStream_t>(cuda_stream)));
+  return FA_OK;
+}
+
 size_t fa_blocksparse_workspace_bytes(int32_t batch, int32_t blockmask_rows, int32_t blockmask_cols) {
   return static_cast<size_t>(batch) * static_cast<size_t>(blockmask_rows) *
          static_cast<size_t>(blockmask_cols) * sizeof(int32_t);

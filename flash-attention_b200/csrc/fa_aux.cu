@@ -1,4 +1,5 @@
 // Small helper kernels: dropout-mask dump (test hook), block-sparse iteration table.
+#include <curand_kernel.h>
 #include "fa_kernels.h"
 
 namespace fa {
@@ -69,7 +70,44 @@ __global__ void bs_table_kernel(int32_t* table, const int32_t* blockmask, const 
   }
 }
 
+// Philox self-check: thread i writes the four output words for (seed, subsequence i, offset).
+// mode 0: this library's round function run `rounds` times with the counter layout of the
+// attention kernels; mode 1: cuRAND's Philox4_32_10 device generator (10 rounds) as an
+// independent implementation of the same generator.
+__global__ void philox_probe_kernel(uint32_t* out, int n, unsigned long long seed,
+                                    unsigned long long offset, int rounds, int mode) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint32_t c[4];
+  if (mode == 1) {
+    curandStatePhilox4_32_10_t st;
+    curand_init(seed, static_cast<unsigned long long>(i), offset, &st);
+    const uint4 r = curand4(&st);
+    c[0] = r.x; c[1] = r.y; c[2] = r.z; c[3] = r.w;
+  } else {
+    const unsigned long long ctr = offset / 4;
+    c[0] = static_cast<uint32_t>(ctr);
+    c[1] = static_cast<uint32_t>(ctr >> 32);
+    c[2] = static_cast<uint32_t>(i);
+    c[3] = 0u;
+    uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
+    for (int r = 0; r < rounds; ++r) {
+      philox_round(c, k0, k1);
+      k0 += 0x9E3779B9u;
+      k1 += 0xBB67AE85u;
+    }
+  }
+  for (int k = 0; k < 4; ++k) out[4 * i + k] = c[k];
+}
+
 }  // namespace
+
+cudaError_t launch_philox_probe(uint32_t* out, int n, unsigned long long seed, unsigned long long offset,
+                                int rounds, int mode, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  philox_probe_kernel<<<(n + 127) / 128, 128, 0, stream>>>(out, n, seed, offset, rounds, mode);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_bs_table(int32_t* table, const int32_t* blockmask, const int32_t* cu_q,
                             const int32_t* cu_k, int batch, int nk, int nr, cudaStream_t stream) {

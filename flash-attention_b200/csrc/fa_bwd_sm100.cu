@@ -425,6 +425,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
       uint32_t pp[32], pds[32];
       const bool need_mask = (n0 + kBN > sk) || (CAUSAL && (n0 + kBN - 1 > m0));
+      // one Philox iteration index per tile: a 128-column tile lies inside one key block
+      int64_t it_tile = 0;
+      if constexpr (DROPOUT) {
+        if constexpr (BLOCKSPARSE) it_tile = bs_it;
+        else it_tile = fa_iter_index(CAUSAL, n0 >> ka.drop.n_shift, ig >> 4, L16, ka.drop.n_shift);
+      }
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t sr[32], dr[32];
@@ -439,11 +445,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
           for (int g2 = 0; g2 < 2; ++g2) {
             const int jg0 = cbase + c * 32 + g2 * 16;
-            int64_t it;
-            if constexpr (BLOCKSPARSE) it = bs_it;
-            else it = fa_iter_index(CAUSAL, jg0 >> ka.drop.n_shift, ig >> 4, L16, ka.drop.n_shift);
-            fa_philox_init(ka.drop, bh_sub, ig, jg0, q0, it, st[2 * g2]);
-            fa_philox_init(ka.drop, bh_sub, ig, jg0, q0 + 1, it, st[2 * g2 + 1]);
+            fa_philox_init(ka.drop, bh_sub, ig, jg0, q0, it_tile, st[2 * g2]);
+            fa_philox_init(ka.drop, bh_sub, ig, jg0, q0 + 1, it_tile, st[2 * g2 + 1]);
           }
 #pragma unroll
           for (int r = 0; r < 7; ++r)
@@ -482,20 +485,16 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             if (!v1) p1 = 0.f;
           }
           if (BLOCKSPARSE && !row_in_layout) { p0 = 0.f; p1 = 0.f; }
-          float g0 = __uint_as_float(dr[i]), g1 = __uint_as_float(dr[i + 1]);
           float k0 = p0, k1 = p1;
           if constexpr (DROPOUT) {
             const uint32_t word = wd[i >> 1];
-            const bool keep0 = (word & 0xffffu) <= thr;
-            const bool keep1 = word < thr_hi;
-            g0 = keep0 ? g0 : 0.f;
-            g1 = keep1 ? g1 : 0.f;
-            k0 = keep0 ? p0 : 0.f;
-            k1 = keep1 ? p1 : 0.f;
+            k0 = ((word & 0xffffu) <= thr) ? p0 : 0.f;
+            k1 = (word < thr_hi) ? p1 : 0.f;
           }
-          // dS = P * (keep * dP - D)
+          // dS = P~ * dP - P * D  (P~ = P where kept, 0 where dropped)
           float s0, s1;
-          unpack_f2(mul2(pack_f2(p0, p1), add2(pack_f2(g0, g1), nd2)), s0, s1);
+          unpack_f2(fma2(pack_f2(k0, k1), pack_f2(__uint_as_float(dr[i]), __uint_as_float(dr[i + 1])),
+                         mul2(pack_f2(p0, p1), nd2)), s0, s1);
           pp[c * 16 + (i >> 1)] = pack_lowp<BF16>(k0, k1);
           pds[c * 16 + (i >> 1)] = pack_lowp<BF16>(s0, s1);
         }

@@ -461,12 +461,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         // multiply chains of different calls overlap.
         uint32_t st[16][4];
         const int q0 = hi_lane ? 2 : 0;
+        // one iteration index per tile: a 128-column tile lies inside one key block
+        int64_t it_index;
+        if constexpr (BLOCKSPARSE) it_index = bs_it;
+        else it_index = fa_iter_index(CAUSAL, col0 >> a.drop.n_shift, ig >> 4, L16, a.drop.n_shift);
 #pragma unroll
         for (int grp = 0; grp < 8; ++grp) {
           const int jg0 = col0 + grp * 16;
-          int64_t it_index;
-          if constexpr (BLOCKSPARSE) it_index = bs_it;
-          else it_index = fa_iter_index(CAUSAL, jg0 >> a.drop.n_shift, ig >> 4, L16, a.drop.n_shift);
           fa_philox_init(a.drop, bh_sub, ig, jg0, q0, it_index, st[2 * grp]);
           fa_philox_init(a.drop, bh_sub, ig, jg0, q0 + 1, it_index, st[2 * grp + 1]);
         }

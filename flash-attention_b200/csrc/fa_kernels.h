@@ -61,6 +61,8 @@ struct BwdLaunch {
 
 cudaError_t launch_fwd(const FwdLaunch& l, cudaStream_t stream);
 cudaError_t launch_bwd(const BwdLaunch& l, cudaStream_t stream);
+cudaError_t launch_philox_probe(uint32_t* out, int n, unsigned long long seed, unsigned long long offset,
+                                int rounds, int mode, cudaStream_t stream);
 cudaError_t launch_bs_table(int32_t* table, const int32_t* blockmask, const int32_t* cu_q,
                             const int32_t* cu_k, int batch, int nk, int nr, cudaStream_t stream);
 cudaError_t launch_dropout_mask(uint8_t* out, int b, int h, const DropoutParams& dp, bool causal,

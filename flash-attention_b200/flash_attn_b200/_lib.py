@@ -25,6 +25,7 @@ EXPORTED_SYMBOLS = (
     "fa_philox_increment",
     "fa_mask_block_n",
     "fa_debug_dropout_mask",
+    "fa_debug_philox",
     "fa_status_string",
     "fa_last_error",
     "fa_device_supported",
@@ -122,6 +123,9 @@ def _load():
                                           ctypes.POINTER(FwdParams), ctypes.c_int32,
                                           ctypes.c_int32, ctypes.c_void_p]
     lib.fa_debug_dropout_mask.restype = ctypes.c_int
+    lib.fa_debug_philox.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_uint64, ctypes.c_uint64,
+                                    ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
+    lib.fa_debug_philox.restype = ctypes.c_int
     lib.fa_status_string.argtypes = [ctypes.c_int]
     lib.fa_status_string.restype = ctypes.c_char_p
     lib.fa_last_error.argtypes = []

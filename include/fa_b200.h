@@ -155,6 +155,14 @@ int fa_debug_dropout_mask(uint8_t* mask_out, int32_t batch_idx, int32_t head_idx
                           const fa_fwd_params* params, int32_t seqlen_q, int32_t seqlen_k,
                           void* cuda_stream);
 
+/* Test hook for the Philox generator of the dropout mask (csrc/flash_attn/src/philox.cuh:7-136):
+ * writes out[4*i .. 4*i+3] = the four output words for key `seed`, subsequence i, counter
+ * offset/4, for i < n.  use_curand = 0 runs this library's round function `rounds` times (the
+ * attention kernels use 7); use_curand = 1 runs cuRAND's Philox4_32_10 device generator instead,
+ * an independent implementation of the same generator at 10 rounds. */
+int fa_debug_philox(uint32_t* out, int32_t n, uint64_t seed, uint64_t offset, int32_t rounds,
+                    int32_t use_curand, void* cuda_stream);
+
 const char* fa_status_string(int status);
 const char* fa_last_error(void);
 
