@@ -276,26 +276,79 @@ def main():
     value = world * flops_step / (ms_step * 1e-3) / 1e12
 
     # ------------------------------------------------------------------ end to end (host buffers)
-    qkv_host = qkv.cpu().pin_memory()
-    dout_host = dout.cpu().pin_memory()
-    out_host = torch.empty((total, HEADS, HEAD_DIM), dtype=torch.float16).pin_memory()
-    dqkv_host = torch.empty_like(qkv_host).pin_memory()
-    qkv_dev = torch.empty_like(qkv)
-    dout_dev = torch.empty_like(dout)
+    # Every step copies its inputs from pinned host memory, runs forward + backward through the
+    # public functional API (autograd) and copies its results (out, dqkv) back to pinned host
+    # memory.  Copies and compute of consecutive steps are pipelined over three streams with two
+    # sets of buffers, as a serving / training loop that feeds the GPU from host memory would do.
+    qkv_host = [qkv.cpu().pin_memory() for _ in range(2)]
+    dout_host = [dout.cpu().pin_memory() for _ in range(2)]
+    out_host = [torch.empty((total, HEADS, HEAD_DIM), dtype=torch.float16).pin_memory() for _ in range(2)]
+    dqkv_host = [torch.empty_like(qkv_host[0]).pin_memory() for _ in range(2)]
+    qkv_dev = [torch.empty_like(qkv) for _ in range(2)]
+    dout_dev = [torch.empty_like(dout) for _ in range(2)]
+    s_h2d, s_d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    ev_in = [torch.cuda.Event() for _ in range(2)]     # inputs of buffer b are on the device
+    ev_done = [torch.cuda.Event() for _ in range(2)]   # compute of buffer b finished
+    ev_out = [torch.cuda.Event() for _ in range(2)]    # results of buffer b are on the host
+    e2e_state = {"i": 0}
 
     def step_e2e():
-        qkv_dev.copy_(qkv_host, non_blocking=True)
-        dout_dev.copy_(dout_host, non_blocking=True)
-        x = qkv_dev.detach().requires_grad_()
+        i = e2e_state["i"]
+        e2e_state["i"] = i + 1
+        bsel = i % 2
+        main = torch.cuda.current_stream()
+        with torch.cuda.stream(s_h2d):
+            if i >= 2:
+                s_h2d.wait_event(ev_done[bsel])       # the step that last used these buffers
+            qkv_dev[bsel].copy_(qkv_host[bsel], non_blocking=True)
+            dout_dev[bsel].copy_(dout_host[bsel], non_blocking=True)
+            ev_in[bsel].record(s_h2d)
+        main.wait_event(ev_in[bsel])
+        x = qkv_dev[bsel].detach().requires_grad_()
         out = flash_attn_unpadded_qkvpacked_func(x, cu, max_s, DROPOUT_P, softmax_scale=scale, causal=False)
-        out.backward(dout_dev)
-        out_host.copy_(out.detach(), non_blocking=True)
-        dqkv_host.copy_(x.grad, non_blocking=True)
+        out.backward(dout_dev[bsel])
+        ev_done[bsel].record(main)
+        with torch.cuda.stream(s_d2h):
+            s_d2h.wait_event(ev_done[bsel])
+            if i >= 2:
+                s_d2h.wait_event(ev_out[bsel])
+            out_d, grad_d = out.detach(), x.grad
+            out_d.record_stream(s_d2h)
+            grad_d.record_stream(s_d2h)
+            out_host[bsel].copy_(out_d, non_blocking=True)
+            dqkv_host[bsel].copy_(grad_d, non_blocking=True)
+            ev_out[bsel].record(s_d2h)
 
-    ms_e2e = timed(step_e2e, max(3, args.steps // 2), 3) if not args.kernels_only else float("nan")
+    def timed_e2e(steps, warmup):
+        for _ in range(warmup):
+            step_e2e()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step_e2e()
+        torch.cuda.current_stream().wait_stream(s_d2h)   # the last results must have reached the host
+        torch.cuda.current_stream().wait_stream(s_h2d)
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            tt = torch.tensor([ms], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = tt.item()
+        return ms
+
+    ms_e2e = timed_e2e(max(4, args.steps), 4) if not args.kernels_only else float("nan")
     e2e_value = world * flops_step / (ms_e2e * 1e-3) / 1e12
-    h2d = qkv_host.numel() * 2 + dout_host.numel() * 2
-    d2h = out_host.numel() * 2 + dqkv_host.numel() * 2
+    h2d = qkv_host[0].numel() * 2 + dout_host[0].numel() * 2
+    d2h = out_host[0].numel() * 2 + dqkv_host[0].numel() * 2
 
     # ------------------------------------------------------------------ kernel-level numbers
     out, lse = fc.fwd(q, k, v, cu, cu, max_s, max_s, DROPOUT_P, scale, False, False, False, None)

@@ -314,18 +314,19 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (!ok) break;
         FA_PROF(3)
         tc_fence_after();
-        if (!Cfg::kDualIssue) {
-          issue_tt(tDV_, smem_p, smem_do + s * Cfg::kTileBytes, t > 0);
-          issue_tt(tDK_, smem_ds, smem_q + s * Cfg::kTileBytes, t > 0);
-        }
         if (!Cfg::kAliasDq && t > 0) {
           ok = mbar_wait(smem_u32(&sh.dq_consumed), (t - 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
         }
         FA_PROF(4)
+        // dQ first: its tile is read out of tensor memory while dV / dK are still running
         issue_dq(tDQ_, smem_ds, smem_k);
         mma_commit(smem_u32(&sh.dq_full));
+        if (!Cfg::kDualIssue) {
+          issue_tt(tDV_, smem_p, smem_do + s * Cfg::kTileBytes, t > 0);
+          issue_tt(tDK_, smem_ds, smem_q + s * Cfg::kTileBytes, t > 0);
+        }
         mma_commit(smem_u32(&sh.pds_free));
         if (!Cfg::kDualIssue) mma_commit(smem_u32(&sh.q_empty[s]));
         FA_PROF(5)
@@ -394,7 +395,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     auto fetch_row_stats = [&](int t) {
       const int ig_n = q_tile(t) * kBM + row;
       const bool valid = ig_n < sq;
-      lse_next = valid ? lse_row[ig_n] * 1.4426950408889634f : INFINITY;
+      lse_next = valid ? lse_row[ig_n] : INFINITY;  // scaled at its first use, one tile later
       d_next = valid ? d_row[ig_n] : 0.f;
       if constexpr (BLOCKSPARSE) {
         bs_next = (ig_n >> 4) < ka.bs_rows16
@@ -408,7 +409,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       FA_PROF(0)
       const int m0 = q_tile(t) * kBM;
       const int ig = m0 + row;
-      const float lse2 = lse_next;
+      const float lse2 = lse_next * 1.4426950408889634f;
       const float d_i = d_next;
       const uint64_t nlse2 = pack_f2(-lse2, -lse2);
       const uint64_t nd2 = pack_f2(-d_i, -d_i);
@@ -499,10 +500,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           pds[c * 16 + (i >> 1)] = pack_lowp<BF16>(s0, s1);
         }
         // the previous tile's products must have finished reading the P~ / dS buffers
+        if (c == 0) { FA_PROF(3) }
         if (c == 0 && t > 0) {
           ok = mbar_wait(smem_u32(&sh.pds_free), (t - 1) & 1, abort_flag);
           ok = __all_sync(0xffffffffu, ok);
         }
+        if (c == 0) { FA_PROF(4) }
         // 32 16-bit values = 4 chunks of 16 bytes of this row in the 64-column panel w
 #pragma unroll
         for (int ch4 = 0; ch4 < 4; ++ch4) {
@@ -517,11 +520,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (!ok) break;
       tc_fence_before();
       mbar_arrive(smem_u32(&sh.sdp_consumed));
-      FA_PROF(3)
-      FA_PROF(4)
+      FA_PROF(6)
       fence_async_smem();
       mbar_arrive(smem_u32(&sh.pds_ready));
-      FA_PROF(5)
+      FA_PROF(7)
     }
     if (w == 0 && row == 0) { FA_PROF_FLUSH(8, nm) }
 
