@@ -221,7 +221,8 @@ int fa_fwd(const fa_fwd_params* p, void* cuda_stream) {
   FA_REQUIRE((reinterpret_cast<uintptr_t>(p->o) & 15) == 0, "o must be 16-byte aligned");
   FA_REQUIRE(p->o_row_stride % 8 == 0 && p->o_head_stride % 8 == 0,
              "o strides must be multiples of 8 elements");
-  if (p->s_dmask) return fail(FA_ERR_UNSUPPORTED, "return_softmax is not built yet");
+  if (p->s_dmask) FA_REQUIRE(p->s_rows >= p->max_seqlen_q && p->s_cols >= p->max_seqlen_k,
+                             "s_dmask must be at least (max_seqlen_q, max_seqlen_k) per (batch, head)");
 
   fa::FwdLaunch l;
   std::memset(&l, 0, sizeof(l));
@@ -241,6 +242,10 @@ int fa_fwd(const fa_fwd_params* p, void* cuda_stream) {
   if (int rc = make_tile_map(&l.tm_v, p->v, l.is_bf16, p->total_k, p->heads, p->head_dim,
                              p->v_row_stride, p->v_head_stride, 128)) return rc;
   FA_CUDA(fa::launch_fwd(l, static_cast<cudaStream_t>(cuda_stream)));
+  if (p->s_dmask)
+    FA_CUDA(fa::launch_sdmask(p->s_dmask, p->s_rows, p->s_cols, p->q, p->k, p->q_row_stride, p->q_head_stride,
+                              p->k_row_stride, p->k_head_stride, l.args, p->max_seqlen_q, p->max_seqlen_k,
+                              l.is_bf16, l.is_causal, l.is_dropout, static_cast<cudaStream_t>(cuda_stream)));
   return FA_OK;
 }
 

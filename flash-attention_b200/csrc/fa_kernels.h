@@ -61,6 +61,10 @@ struct BwdLaunch {
 
 cudaError_t launch_fwd(const FwdLaunch& l, cudaStream_t stream);
 cudaError_t launch_bwd(const BwdLaunch& l, cudaStream_t stream);
+cudaError_t launch_sdmask(void* s_out, int64_t s_rows, int64_t s_cols, const void* q, const void* k,
+                          int64_t q_row_stride, int64_t q_head_stride, int64_t k_row_stride,
+                          int64_t k_head_stride, const KernelArgs& a, int max_seqlen_q, int max_seqlen_k,
+                          bool bf16, bool causal, bool dropout, cudaStream_t stream);
 cudaError_t launch_philox_probe(uint32_t* out, int n, unsigned long long seed, unsigned long long offset,
                                 int rounds, int mode, cudaStream_t stream);
 cudaError_t launch_bs_table(int32_t* table, const int32_t* blockmask, const int32_t* cu_q,

@@ -129,8 +129,6 @@ def _run_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_
              softmax_scale, zero_tensors, is_causal, return_softmax, gen, blockmask=None):
     batch, total_q, total_k, heads, d = _check_qkv(q, k, v, cu_seqlens_q, cu_seqlens_k)
     _require(p_dropout < 1.0, "p_dropout must be < 1")
-    if return_softmax:
-        raise RuntimeError("fa_b200: return_softmax is not available")
     sparse = blockmask is not None
     if sparse:
         _require(not is_causal, "block-sparse attention does not support causal")
@@ -153,13 +151,21 @@ def _run_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_
         p = FwdParams()
         _fill_fwd(p, q, k, v, o, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
                   p_dropout, softmax_scale, is_causal, seed, offset)
+        s_dmask = None
+        if return_softmax:
+            # (batch, heads, seqlen_q rounded to 16, seqlen_k rounded as the reference does,
+            # csrc/flash_attn/fmha_api.cpp:232-240, :253); zero outside the sequences
+            base = 256 if sparse else (128 if (d == 128 and p_dropout > 0) else 256)
+            sk_r = 128 if (max_seqlen_k <= 128 and not sparse) else (256 if max_seqlen_k <= 256 else _round_up(int(max_seqlen_k), base))
+            s_dmask = torch.zeros((batch, heads, lse_len, sk_r), dtype=q.dtype, device=q.device)
+            p.s_dmask, p.s_rows, p.s_cols = s_dmask.data_ptr(), lse_len, sk_r
         if sparse:
             ws = _bs_workspace(q.device, batch, blockmask)
             p.blockmask = blockmask.data_ptr()
             p.blockmask_rows, p.blockmask_cols = blockmask.shape
             p.bs_workspace, p.bs_workspace_bytes = ws.data_ptr(), ws.numel()
         check(lib.fa_fwd(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
-    return [o, lse]
+    return [o, lse, s_dmask] if return_softmax else [o, lse]
 
 
 def fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale,

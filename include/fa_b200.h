@@ -48,8 +48,11 @@ typedef struct fa_fwd_params {
    * blockmask_rows >= ceil(max_seqlen_k / 256) key blocks and
    * blockmask_cols >= ceil(max_seqlen_q / 16) list slots; NULL for dense attention. */
   const int32_t* blockmask;
-  /* Optional [batch, heads, s_rows, s_cols] 16-bit output of the softmax probabilities with the
-   * sign bit marking dropped entries (return_softmax); NULL to skip. */
+  /* Optional [batch, heads, s_rows, s_cols] 16-bit output (return_softmax, a test aid): the softmax
+   * probability of every (query, key) pair with the sign bit set where dropout dropped it, in
+   * plain row-major order (the reference writes un-normalised values in its MMA fragment order,
+   * csrc/flash_attn/src/fmha/gmem_tile.h:289-405).  Entries outside the sequences are not written.
+   * Recomputed on the CUDA cores after the attention kernel: O(seqlen^2 * d), for tests.  NULL to skip. */
   void* s_dmask;
   int64_t s_rows, s_cols;
   /* strides in elements */

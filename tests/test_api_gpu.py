@@ -113,3 +113,37 @@ def test_flash_attention_module_three_input_paths():
     mha = FlashMHA(256, 4, use_rotary_emb="1d", causal=True, device="cuda", dtype=torch.float16)
     y, _ = mha(torch.randn(2, 64, 256, device="cuda", dtype=torch.float16), key_padding_mask=None)
     assert y.shape == (2, 64, 256) and not torch.isnan(y).any()
+
+
+@pytest.mark.parametrize("causal,p", [(False, 0.0), (True, 0.2)])
+def test_return_attn_probs_gives_probabilities_and_dropout_signs(causal, p):
+    """return_attn_probs=True: S_dmask holds the softmax probabilities in (batch, heads, seqlen_q,
+    seqlen_k) order with a negative sign where dropout dropped the entry."""
+    import numpy as np
+    from flash_attn_b200.flash_attn_interface import flash_attn_unpadded_qkvpacked_func
+    seqlens = [150, 260]
+    heads, d = 2, 64
+    q, k, v, dout, cu, _ = U.make_varlen(seqlens, seqlens, heads, d, torch.float16, seed=53)
+    qkv = torch.stack([q, k, v], 1)
+    seed = 77
+    torch.cuda.manual_seed(seed)
+    out, lse, s_dmask = flash_attn_unpadded_qkvpacked_func(qkv, cu, 260, p, causal=causal, return_attn_probs=True)
+    torch.cuda.synchronize()
+    assert s_dmask.shape == (2, heads, 272, 512) and lse.shape == (2, heads, 272)
+    n = orc.mask_block_n(d, 260)
+    start = 0
+    for b, s in enumerate(seqlens):
+        qb, kb = q[start:start + s].float().cpu(), k[start:start + s].float().cpu()
+        scores = torch.einsum("thd,shd->hts", qb, kb) * d ** -0.5
+        if causal:
+            scores = scores.masked_fill(torch.triu(torch.ones(s, s, dtype=torch.bool), 1), float("-inf"))
+        probs = torch.softmax(scores, dim=-1)
+        got = s_dmask[b, :, :s, :s].float().cpu()
+        assert (got.abs() - probs).abs().max().item() < 2e-3
+        if p > 0:
+            keep = np.stack([orc.dropout_keep_mask(seed, 0, b, h, heads, s, s, p, n, causal) for h in range(heads)])
+            visible = probs.numpy() > 1e-6
+            np.testing.assert_array_equal((got.numpy() >= 0)[visible], keep[visible])
+        else:
+            assert (got >= 0).all()
+        start += s
