@@ -122,6 +122,10 @@ void fill_dropout(const fa_fwd_params* p, fa::KernelArgs* a) {
   a->drop.key0 = static_cast<uint32_t>(p->philox_seed);
   a->drop.key1 = static_cast<uint32_t>(p->philox_seed >> 32);
   a->drop.counter_base = p->philox_offset / 4;
+  for (int r = 0; r < 7; ++r) {
+    a->drop.rk0[r] = a->drop.key0 + static_cast<uint32_t>(r) * 0x9E3779B9u;
+    a->drop.rk1[r] = a->drop.key1 + static_cast<uint32_t>(r) * 0xBB67AE85u;
+  }
   a->drop.threshold = static_cast<uint32_t>(
       static_cast<uint16_t>(std::floor(static_cast<double>(p_keep) * 65535.0)));
   a->drop.n_shift = fa_mask_block_n(p->head_dim, p->max_seqlen_k, p->blockmask != nullptr) == 128 ? 7 : 8;
@@ -241,6 +245,7 @@ int fa_fwd(const fa_fwd_params* p, void* cuda_stream) {
                              p->k_row_stride, p->k_head_stride, 128)) return rc;
   if (int rc = make_tile_map(&l.tm_v, p->v, l.is_bf16, p->total_k, p->heads, p->head_dim,
                              p->v_row_stride, p->v_head_stride, 128)) return rc;
+  if (p->status) FA_CUDA(cudaMemsetAsync(p->status, 0, sizeof(int32_t), static_cast<cudaStream_t>(cuda_stream)));
   FA_CUDA(fa::launch_fwd(l, static_cast<cudaStream_t>(cuda_stream)));
   if (p->s_dmask)
     FA_CUDA(fa::launch_sdmask(p->s_dmask, p->s_rows, p->s_cols, p->q, p->k, p->q_row_stride, p->q_head_stride,
@@ -334,6 +339,7 @@ int fa_bwd(const fa_bwd_params* p, void* cuda_stream) {
   if (int rc = make_tile_map(&l.tm_do, p->dout, l.is_bf16, f->total_q, f->heads, f->head_dim,
                              a.do_row_stride, a.do_head_stride, 128)) return rc;
   if (int rc = make_accum_map(&l.tm_dq, a.dq_accum, f->total_q, f->heads, l.dpad)) return rc;
+  if (f->status) FA_CUDA(cudaMemsetAsync(f->status, 0, sizeof(int32_t), static_cast<cudaStream_t>(cuda_stream)));
   FA_CUDA(fa::launch_bwd(l, static_cast<cudaStream_t>(cuda_stream)));
   return FA_OK;
 }
@@ -456,6 +462,7 @@ int fa_bwd_static_scratch(const fa_bwd_params* p, void* cuda_stream) {
   if (int rc = encode_tile_map(&l.tm_do, p->dout, l.is_bf16, f->total_q, f->heads, f->head_dim,
                                a.do_row_stride, a.do_head_stride)) return rc;
   if (int rc = make_accum_map(&l.tm_dq, a.dq_accum, f->total_q, f->heads, l.dpad)) return rc;
+  if (f->status) FA_CUDA(cudaMemsetAsync(f->status, 0, sizeof(int32_t), static_cast<cudaStream_t>(cuda_stream)));
   FA_CUDA(fa::launch_bwd(l, static_cast<cudaStream_t>(cuda_stream)));
   return FA_OK;
 }

@@ -131,6 +131,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const int sk = ka.cu_seqlens_k[b + 1] - k_start;
   const int n0 = nt * kBN;
   if (n0 >= sk) return;
+  // fail fast: once a CTA of this launch has abandoned a wait, the remaining CTAs do not start
+  if (ka.status && *reinterpret_cast<volatile int32_t*>(ka.status) != 0) return;
 
   const int m_tiles = (sq + kBM - 1) / kBM;
   const int m_begin = CAUSAL ? min(m_tiles, n0 / kBM) : 0;
@@ -383,8 +385,6 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const bool hi_lane = (row & 8) != 0;
     const uint32_t thr = ka.drop.threshold;
     const uint32_t thr_hi = (thr + 1u) << 16;
-    PhiloxKeys keys;
-    if constexpr (DROPOUT) keys.init(ka.drop.key0, ka.drop.key1);
     const int cbase = n0 + w * 64;  // first key column of this thread
     bool ok = true;
     FA_PROF_DECL
@@ -452,7 +452,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
           for (int r = 0; r < 7; ++r)
 #pragma unroll
-            for (int k4 = 0; k4 < 4; ++k4) philox_round(st[k4], keys.k0[r], keys.k1[r]);
+            for (int k4 = 0; k4 < 4; ++k4) philox_round(st[k4], ka.drop.rk0[r], ka.drop.rk1[r]);
 #pragma unroll
           for (int g2 = 0; g2 < 2; ++g2) {
             const uint32_t(&ca)[4] = st[2 * g2];
@@ -628,7 +628,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   __syncthreads();
   if (warp == 12) {
     tmem_dealloc(tmem, 512);
-    if (lane == 0 && sh.abort_flag && ka.status) atomicExch(ka.status + 1, 1);
+    if (lane == 0 && sh.abort_flag && ka.status) {
+      atomicExch(ka.status, 1);      // launch-local: stops CTAs that have not started yet
+      atomicExch(ka.status + 3, 1);  // sticky: read by the host
+    }
   }
 }
 

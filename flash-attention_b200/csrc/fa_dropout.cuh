@@ -27,6 +27,7 @@ struct DropoutParams {
   int32_t n_shift;         // log2(N): 7 or 8
   int32_t heads_total;     // H used in the subsequence
   int32_t head_offset;
+  uint32_t rk0[7], rk1[7]; // round keys key + r * (0x9E3779B9, 0xBB67AE85), r = 0..6 (kernel constants)
 };
 
 __host__ __device__ __forceinline__ uint64_t mul_wide_u32(uint32_t a, uint32_t b) {

@@ -32,7 +32,7 @@ __device__ __forceinline__ bool elect_one() {
 // ---------------------------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------------------------
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about one second at 2 GHz
+constexpr long long WAIT_LIMIT_CYCLES = 200000000LL;  // about 0.1 s at 2 GHz; a healthy wait lasts microseconds
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

@@ -31,7 +31,7 @@ def check_device_status(device=None):
     if buf is None:
         return
     val = buf[:4].cpu().tolist()
-    if any(val):
+    if val[2] or val[3]:
         buf.zero_()
         raise RuntimeError("fa_b200: a kernel abandoned a bounded wait (status %s)" % val)
 
