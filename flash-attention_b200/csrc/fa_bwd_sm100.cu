@@ -254,7 +254,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const uint32_t tDV_ = tmem + Cfg::kTmemDV, tDK_ = tmem + Cfg::kTmemDK, tDQ_ = tmem + Cfg::kTmemDQ;
 
   if (warp >= 12) {
-    reg_dealloc<72>();
+    // register split (per thread): d = 64: 192 compute / 72 dQ / 56 here; d = 128: 176 / 88 / 72
+    if constexpr (D == 64) reg_dealloc<56>(); else reg_dealloc<72>();
     if (warp == 12 && lane == 0) {
       // -------------------------------------------------------------- TMA producer
       tma_prefetch_desc(&tm_q);
@@ -370,7 +371,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   } else if (warp < 8) {
     // ------------------------------------------------------------------ compute groups
     // group w (0 / 1) owns key columns [64 w, 64 w + 64) of the tile; one thread per query row
-    reg_alloc<176>();
+    if constexpr (D == 64) reg_alloc<192>(); else reg_alloc<176>();
     const int w = warp >> 2;
     const int row = tid & 127;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -424,7 +425,6 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       FA_PROF(2)
       tc_fence_after();
 
-      uint32_t pp[32], pds[32];
       const bool need_mask = (n0 + kBN > sk) || (CAUSAL && (n0 + kBN - 1 > m0));
       // one Philox iteration index per tile: a 128-column tile lies inside one key block
       int64_t it_tile = 0;
@@ -432,11 +432,29 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if constexpr (BLOCKSPARSE) it_tile = bs_it;
         else it_tile = fa_iter_index(CAUSAL, n0 >> ka.drop.n_shift, ig >> 4, L16, ka.drop.n_shift);
       }
+      // This thread's 64 scores and 64 dP values go to registers at once, so that the next tile's
+      // S and dP products can overwrite tensor memory while this tile is still being processed.
+      // (d = 64 only: at d = 128 the next dP waits for the dQ read-out anyway, and the registers
+      // are better spent elsewhere, so there the values are loaded 32 columns at a time.)
+      constexpr bool kEarly = (D == 64);
+      uint32_t sr_all[kEarly ? 2 : 1][32], dr_all[kEarly ? 2 : 1][32];
+      if constexpr (kEarly) {
+        tmem_ld32(tS, sr_all[0]);
+        tmem_ld32(tS + 32, sr_all[1]);
+        tmem_ld32(tDP, dr_all[0]);
+        tmem_ld32(tDP + 32, dr_all[1]);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&sh.sdp_consumed));
+      }
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t sr[32], dr[32];
-        tmem_ld32(tS + c * 32, sr);
-        tmem_ld32(tDP + c * 32, dr);
+        uint32_t(&sr)[32] = sr_all[kEarly ? c : 0];
+        uint32_t(&dr)[32] = dr_all[kEarly ? c : 0];
+        if constexpr (!kEarly) {
+          tmem_ld32(tS + c * 32, sr);
+          tmem_ld32(tDP + c * 32, dr);
+        }
 
         // keep words of the 16 column pairs of this chunk (two 16-column groups)
         uint32_t wd[16];
@@ -470,8 +488,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             wg[3] = hi_lane ? kb0 : rb0; wg[7] = hi_lane ? kb1 : rb1;
           }
         }
-        tmem_wait_ld();
 
+        uint32_t pp[16], pds[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float p0, p1;
@@ -496,8 +514,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           float s0, s1;
           unpack_f2(fma2(pack_f2(k0, k1), pack_f2(__uint_as_float(dr[i]), __uint_as_float(dr[i + 1])),
                          mul2(pack_f2(p0, p1), nd2)), s0, s1);
-          pp[c * 16 + (i >> 1)] = pack_lowp<BF16>(k0, k1);
-          pds[c * 16 + (i >> 1)] = pack_lowp<BF16>(s0, s1);
+          pp[i >> 1] = pack_lowp<BF16>(k0, k1);
+          pds[i >> 1] = pack_lowp<BF16>(s0, s1);
         }
         // the previous tile's products must have finished reading the P~ / dS buffers
         if (c == 0) { FA_PROF(3) }
@@ -512,14 +530,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           const int ch = c * 4 + ch4;
           const uint32_t off = w * 16384 + row * 128 + ((ch ^ (row & 7)) << 4);
           *reinterpret_cast<uint4*>(p_ptr + off) =
-              make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
+              make_uint4(pp[4 * ch4], pp[4 * ch4 + 1], pp[4 * ch4 + 2], pp[4 * ch4 + 3]);
           *reinterpret_cast<uint4*>(ds_ptr + off) =
-              make_uint4(pds[4 * ch], pds[4 * ch + 1], pds[4 * ch + 2], pds[4 * ch + 3]);
+              make_uint4(pds[4 * ch4], pds[4 * ch4 + 1], pds[4 * ch4 + 2], pds[4 * ch4 + 3]);
         }
       }
       if (!ok) break;
-      tc_fence_before();
-      mbar_arrive(smem_u32(&sh.sdp_consumed));
       FA_PROF(6)
       fence_async_smem();
       mbar_arrive(smem_u32(&sh.pds_ready));
@@ -563,7 +579,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     // dQ tile: tensor memory -> registers -> swizzled fp32 staging in shared memory -> one TMA
     // reduce-add per [128 rows x 32 columns] box into the fp32 accumulator.  Rows past the end of
     // the sequence hold exact zeros (their P is zero), rows past the tensor are clipped by TMA.
-    reg_dealloc<88>();
+    if constexpr (D == 64) reg_dealloc<72>(); else reg_dealloc<88>();
     const int row = tid - 256;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tDQ = tDQ_ + lane_sel;
@@ -588,25 +604,30 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       tc_fence_after();
 #pragma unroll
       for (int half = 0; half < D / 64; ++half) {
-        uint32_t r0[32], r1[32];
-        tmem_ld32(tDQ + half * 64, r0);
-        tmem_ld32(tDQ + half * 64 + 32, r1);
-        tmem_wait_ld();
-        if (half == D / 64 - 1) {
-          tc_fence_before();
-          mbar_arrive(smem_u32(&sh.dq_consumed));
-        }
-        // the staging buffer is free once the previous reduce has read it
-        if (row == 0 && pending) bulk_wait_read();
-        ok = group_sync();
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          const uint32_t off = row * 128 + ((ch ^ (row & 7)) << 4);
-          *reinterpret_cast<uint4*>(dq_stage + off) = make_uint4(r0[4 * ch], r0[4 * ch + 1], r0[4 * ch + 2], r0[4 * ch + 3]);
-          *reinterpret_cast<uint4*>(dq_stage + 16384 + off) = make_uint4(r1[4 * ch], r1[4 * ch + 1], r1[4 * ch + 2], r1[4 * ch + 3]);
+        for (int bx = 0; bx < 2; ++bx) {
+          uint32_t r[32];
+          tmem_ld32(tDQ + half * 64 + bx * 32, r);
+          tmem_wait_ld();
+          if (half == D / 64 - 1 && bx == 1) {
+            tc_fence_before();
+            mbar_arrive(smem_u32(&sh.dq_consumed));
+          }
+          if (bx == 0) {
+            // the staging buffer is free once the previous reduce has read it
+            if (row == 0 && pending) bulk_wait_read();
+            ok = group_sync();
+            ok = __all_sync(0xffffffffu, ok);
+          }
+          if (ok) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+              const uint32_t off = bx * 16384 + row * 128 + ((ch ^ (row & 7)) << 4);
+              *reinterpret_cast<uint4*>(dq_stage + off) = make_uint4(r[4 * ch], r[4 * ch + 1], r[4 * ch + 2], r[4 * ch + 3]);
+            }
+          }
         }
+        if (!ok) break;
         fence_async_smem();
         ok = group_sync();
         ok = __all_sync(0xffffffffu, ok);
