@@ -140,6 +140,9 @@ int setup_blocksparse(const fa_fwd_params* p, fa::KernelArgs* a, cudaStream_t st
   const int nr = p->blockmask_cols;
   FA_REQUIRE(nk >= round_up(p->max_seqlen_k, 256) / 256, "blockmask has too few key-block rows");
   FA_REQUIRE(nr >= round_up(p->max_seqlen_q, 16) / 16, "blockmask rows are too short for max_seqlen_q");
+  // the kernels keep a per-CTA list of visited 128-row tiles in shared memory (1024 entries)
+  FA_REQUIRE(p->max_seqlen_q <= 131072 && p->max_seqlen_k <= 131072,
+             "block-sparse attention supports sequences up to 131072");
   const size_t need = fa_blocksparse_workspace_bytes(p->batch, nk, nr);
   if (p->bs_workspace == nullptr || p->bs_workspace_bytes < need)
     return fail(FA_ERR_WORKSPACE, "bs_workspace must hold " + std::to_string(need) + " bytes");

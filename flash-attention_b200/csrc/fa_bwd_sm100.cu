@@ -383,9 +383,13 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const float* lse_row = ka.lse + (static_cast<int64_t>(b) * ka.heads + h) * ka.lse_stride;
     const float* d_row = a.softmax_d + (static_cast<int64_t>(b) * ka.heads + h) * ka.lse_stride;
     const uint64_t c2 = pack_f2(ka.scale_log2, ka.scale_log2);
-    const bool hi_lane = (row & 8) != 0;
-    const uint32_t thr = ka.drop.threshold;
-    const uint32_t thr_hi = (thr + 1u) << 16;
+    // dropout: per-lane generator state (lanes l and l ^ 8 share every Philox call)
+    LanePhilox lp;
+    float thr_term = 0.f;
+    if constexpr (DROPOUT) {
+      lp.init(ka.drop, bh_sub, row);
+      thr_term = fa_keep_thr_term(ka.drop.threshold);
+    }
     const int cbase = n0 + w * 64;  // first key column of this thread
     bool ok = true;
     FA_PROF_DECL
@@ -418,6 +422,30 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const bool row_in_layout = !BLOCKSPARSE || bs_it >= 0;
       if (t + 1 < nm) fetch_row_stats(t + 1);
 
+      // Keep words of this thread's 64 columns (wd[p] covers columns 2p, 2p + 1).  They do not depend
+      // on the scores, so they are drawn before the wait for S and dP: eight independent Philox
+      // calls (4 column groups x 2 quarters) with their rounds interleaved.
+      uint32_t wd[DROPOUT ? 32 : 1];
+      if constexpr (DROPOUT) {
+        // one Philox iteration index per tile: a 128-column tile lies inside one key block
+        int64_t it_tile;
+        if constexpr (BLOCKSPARSE) it_tile = bs_it;
+        else it_tile = fa_iter_index(CAUSAL, n0 >> ka.drop.n_shift, ig >> 4, L16, ka.drop.n_shift);
+        lp.set_tile(ka.drop, it_tile, n0);
+        uint32_t st[8][4];
+#pragma unroll
+        for (int g4 = 0; g4 < 4; ++g4) {
+          lp.start(w * 4 + g4, 0, st[2 * g4]);
+          lp.start(w * 4 + g4, 1, st[2 * g4 + 1]);
+        }
+#pragma unroll
+        for (int r = 0; r < 7; ++r)
+#pragma unroll
+          for (int k8 = 0; k8 < 8; ++k8) lp.round(st[k8], r);
+#pragma unroll
+        for (int g4 = 0; g4 < 4; ++g4) lp.finish(st[2 * g4], st[2 * g4 + 1], wd + g4 * 8);
+      }
+
       FA_PROF(1)
       ok = mbar_wait(smem_u32(&sh.sdp_full), t & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
@@ -426,12 +454,6 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       tc_fence_after();
 
       const bool need_mask = (n0 + kBN > sk) || (CAUSAL && (n0 + kBN - 1 > m0));
-      // one Philox iteration index per tile: a 128-column tile lies inside one key block
-      int64_t it_tile = 0;
-      if constexpr (DROPOUT) {
-        if constexpr (BLOCKSPARSE) it_tile = bs_it;
-        else it_tile = fa_iter_index(CAUSAL, n0 >> ka.drop.n_shift, ig >> 4, L16, ka.drop.n_shift);
-      }
       // This thread's 64 scores and 64 dP values go to registers at once, so that the next tile's
       // S and dP products can overwrite tensor memory while this tile is still being processed.
       // (d = 64 only: at d = 128 the next dP waits for the dQ read-out anyway, and the registers
@@ -456,39 +478,6 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           tmem_ld32(tDP + c * 32, dr);
         }
 
-        // keep words of the 16 column pairs of this chunk (two 16-column groups)
-        uint32_t wd[16];
-        if constexpr (DROPOUT) {
-          uint32_t st[4][4];
-          const int q0 = hi_lane ? 2 : 0;
-#pragma unroll
-          for (int g2 = 0; g2 < 2; ++g2) {
-            const int jg0 = cbase + c * 32 + g2 * 16;
-            fa_philox_init(ka.drop, bh_sub, ig, jg0, q0, it_tile, st[2 * g2]);
-            fa_philox_init(ka.drop, bh_sub, ig, jg0, q0 + 1, it_tile, st[2 * g2 + 1]);
-          }
-#pragma unroll
-          for (int r = 0; r < 7; ++r)
-#pragma unroll
-            for (int k4 = 0; k4 < 4; ++k4) philox_round(st[k4], ka.drop.rk0[r], ka.drop.rk1[r]);
-#pragma unroll
-          for (int g2 = 0; g2 < 2; ++g2) {
-            const uint32_t(&ca)[4] = st[2 * g2];
-            const uint32_t(&cb)[4] = st[2 * g2 + 1];
-            const uint32_t ka0 = hi_lane ? ca[2] : ca[0], ka1 = hi_lane ? ca[3] : ca[1];
-            const uint32_t kb0 = hi_lane ? cb[2] : cb[0], kb1 = hi_lane ? cb[3] : cb[1];
-            const uint32_t ra0 = __shfl_xor_sync(0xffffffffu, hi_lane ? ca[0] : ca[2], 8);
-            const uint32_t ra1 = __shfl_xor_sync(0xffffffffu, hi_lane ? ca[1] : ca[3], 8);
-            const uint32_t rb0 = __shfl_xor_sync(0xffffffffu, hi_lane ? cb[0] : cb[2], 8);
-            const uint32_t rb1 = __shfl_xor_sync(0xffffffffu, hi_lane ? cb[1] : cb[3], 8);
-            uint32_t* wg = wd + g2 * 8;
-            wg[0] = hi_lane ? ra0 : ka0; wg[4] = hi_lane ? ra1 : ka1;
-            wg[1] = hi_lane ? rb0 : kb0; wg[5] = hi_lane ? rb1 : kb1;
-            wg[2] = hi_lane ? ka0 : ra0; wg[6] = hi_lane ? ka1 : ra1;
-            wg[3] = hi_lane ? kb0 : rb0; wg[7] = hi_lane ? kb1 : rb1;
-          }
-        }
-
         uint32_t pp[16], pds[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -505,14 +494,15 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           }
           if (BLOCKSPARSE && !row_in_layout) { p0 = 0.f; p1 = 0.f; }
           float k0 = p0, k1 = p1;
+          uint64_t k01 = pack_f2(p0, p1);
           if constexpr (DROPOUT) {
-            const uint32_t word = wd[i >> 1];
-            k0 = ((word & 0xffffu) <= thr) ? p0 : 0.f;
-            k1 = (word < thr_hi) ? p1 : 0.f;
+            const uint32_t word = wd[c * 16 + (i >> 1)];
+            k01 = mul2(k01, pack_f2(fa_keep_factor_lo(word, thr_term), fa_keep_factor_hi(word, thr_term)));
+            unpack_f2(k01, k0, k1);
           }
           // dS = P~ * dP - P * D  (P~ = P where kept, 0 where dropped)
           float s0, s1;
-          unpack_f2(fma2(pack_f2(k0, k1), pack_f2(__uint_as_float(dr[i]), __uint_as_float(dr[i + 1])),
+          unpack_f2(fma2(k01, pack_f2(__uint_as_float(dr[i]), __uint_as_float(dr[i + 1])),
                          mul2(pack_f2(p0, p1), nd2)), s0, s1);
           pp[i >> 1] = pack_lowp<BF16>(k0, k1);
           pds[i >> 1] = pack_lowp<BF16>(s0, s1);

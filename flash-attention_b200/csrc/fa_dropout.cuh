@@ -161,4 +161,110 @@ __host__ __device__ __forceinline__ void fa_philox_init(const DropoutParams& dp,
   c[3] = static_cast<uint32_t>(subseq >> 32);
 }
 
+#ifdef __CUDACC__
+// ---------------------------------------------------------------------------------------------
+// Row-per-thread mask generation (the layout of the attention kernels: lane = query row).
+//
+// Rows r and r + 8 of a 16-row block share every Philox call: output words 0, 1 belong to the row
+// with (r % 16) < 8 and words 2, 3 to the row 8 below.  A lane and its partner 8 lanes away each run
+// two of the four calls (quarters) of a 16-column group and exchange the half they do not need.
+// So that both lanes send the same registers, the lane of the lower row runs the generator on the
+// state (c0, c1, c2, c3) and the lane of the upper row on the mirrored state (c2, c3, c0, c1): one
+// round maps the mirrored state to the mirror of the next state when the two multipliers and the
+// two round keys trade places, which makes them per-lane registers.  Either way words 0, 1 of the
+// state are the lane's own and words 2, 3 go to the partner.
+struct LanePhilox {
+  uint32_t mul_a, mul_b;       // multiplier of state word 0 / of state word 2
+  uint32_t key_a[7], key_b[7];  // round keys folded into the new word 0 / the new word 2
+  uint32_t base[4];             // state before the per-call subsequence offset is added
+  uint32_t step_a, step_b;      // 1 on the state word that holds the subsequence's low word
+  bool upper;                   // this lane owns the row with (r % 16) >= 8
+
+  // i: query row of this lane.  The subsequence's low byte is (column group % 8) * 32 + (i % 8) * 4
+  // + quarter; a lane runs quarters 0, 1 (lower row) or 2, 3 (upper row).
+  __device__ __forceinline__ void init(const DropoutParams& dp, int64_t bh_sub, int32_t i) {
+    upper = (i & 8) != 0;
+    mul_a = upper ? 0xCD9E8D57u : 0xD2511F53u;
+    mul_b = upper ? 0xD2511F53u : 0xCD9E8D57u;
+#pragma unroll
+    for (int r = 0; r < 7; ++r) {
+      const uint32_t k0 = dp.key0 + static_cast<uint32_t>(r) * 0x9E3779B9u;
+      const uint32_t k1 = dp.key1 + static_cast<uint32_t>(r) * 0xBB67AE85u;
+      key_a[r] = upper ? k1 : k0;
+      key_b[r] = upper ? k0 : k1;
+    }
+    const uint64_t sub = static_cast<uint64_t>(bh_sub) + (i & 7) * 4 + (upper ? 2 : 0);
+    base[upper ? 0 : 2] = static_cast<uint32_t>(sub);
+    base[upper ? 1 : 3] = static_cast<uint32_t>(sub >> 32);
+    step_a = upper ? 1u : 0u;
+    step_b = upper ? 0u : 1u;
+  }
+  // Counter of the calls of one 128-column tile: iteration index of (key block, 16-row block) and the
+  // 128-column half of the key block the tile is (fa_dropout_words above).
+  __device__ __forceinline__ void set_tile(const DropoutParams& dp, int64_t iter_index, int32_t col0) {
+    const int32_t n_mask = (1 << dp.n_shift) - 1;
+    const uint64_t ctr = dp.counter_base + static_cast<uint64_t>(iter_index << (dp.n_shift - 7)) +
+                         static_cast<uint64_t>((col0 & n_mask) >> 7);
+    base[upper ? 2 : 0] = static_cast<uint32_t>(ctr);
+    base[upper ? 3 : 1] = static_cast<uint32_t>(ctr >> 32);
+  }
+  // State of the call for 16-column group `grp` (0..7 within the tile) and quarter offset qq (0 / 1).
+  // The offset never carries: the low byte of the subsequence base is below 32.
+  __device__ __forceinline__ void start(int grp, int qq, uint32_t (&s)[4]) const {
+    const uint32_t off = static_cast<uint32_t>(grp * 32 + qq);
+    s[0] = base[0] + off * step_a;
+    s[1] = base[1];
+    s[2] = base[2] + off * step_b;
+    s[3] = base[3];
+  }
+  __device__ __forceinline__ void round(uint32_t (&s)[4], int r) const {
+    const uint64_t p0 = mul_wide_u32(mul_a, s[0]);
+    const uint64_t p1 = mul_wide_u32(mul_b, s[2]);
+    const uint32_t n0 = static_cast<uint32_t>(p1 >> 32) ^ s[1] ^ key_a[r];
+    const uint32_t n2 = static_cast<uint32_t>(p0 >> 32) ^ s[3] ^ key_b[r];
+    s[1] = static_cast<uint32_t>(p1);
+    s[3] = static_cast<uint32_t>(p0);
+    s[0] = n0;
+    s[2] = n2;
+  }
+  // After seven rounds of the calls (grp, 0) and (grp, 1): the eight keep words of the lane's row
+  // for that group, wd[p] covering columns 2p, 2p + 1 (low half = even column).
+  __device__ __forceinline__ void finish(const uint32_t (&sa)[4], const uint32_t (&sb)[4],
+                                         uint32_t* wd) const {
+    const uint32_t ra0 = __shfl_xor_sync(0xffffffffu, sa[2], 8);
+    const uint32_t ra1 = __shfl_xor_sync(0xffffffffu, sa[3], 8);
+    const uint32_t rb0 = __shfl_xor_sync(0xffffffffu, sb[2], 8);
+    const uint32_t rb1 = __shfl_xor_sync(0xffffffffu, sb[3], 8);
+    // quarter q: first word -> pair q (columns 2q, 2q+1), second word -> pair q + 4 (columns 2q+8, 2q+9)
+    wd[0] = upper ? ra0 : sa[0]; wd[4] = upper ? ra1 : sa[1];
+    wd[1] = upper ? rb0 : sb[0]; wd[5] = upper ? rb1 : sb[1];
+    wd[2] = upper ? sa[0] : ra0; wd[6] = upper ? sa[1] : ra1;
+    wd[3] = upper ? sb[0] : rb0; wd[7] = upper ? sb[1] : rb1;
+  }
+};
+
+// Keep factors (1.0f kept / 0.0f dropped) of the two 16-bit values of a keep word, without integer
+// compares: the 16 bits become the top mantissa bits of a float in [0.5, 2) (bytes 0x3F | hi | lo |
+// filler, a monotone map), and a saturating fma against the threshold mapped the same way gives
+// sat((T - x) * 2^24), which is exactly 1 when x < T and 0 otherwise (both are multiples of 2^-24).
+//   thr_term = float(0x3F000000 + ((threshold + 1) << 8)) * 2^24
+__device__ __forceinline__ float fa_keep_thr_term(uint32_t threshold) {
+  return __uint_as_float(0x3F000000u + ((threshold + 1u) << 8)) * 16777216.f;
+}
+__device__ __forceinline__ float fa_keep_factor_lo(uint32_t w, float thr_term) {
+  uint32_t f;
+  float k;
+  asm("prmt.b32 %0, %1, %2, 0x7104;" : "=r"(f) : "r"(w), "r"(0x3F000000u));
+  asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(k) : "f"(__uint_as_float(f)), "f"(-16777216.f), "f"(thr_term));
+  return k;
+}
+__device__ __forceinline__ float fa_keep_factor_hi(uint32_t w, float thr_term) {
+  uint32_t f;
+  float k;
+  asm("prmt.b32 %0, %1, %2, 0x7321;" : "=r"(f) : "r"(w), "r"(0x3F000000u));
+  asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(k) : "f"(__uint_as_float(f)), "f"(-16777216.f), "f"(thr_term));
+  return k;
+}
+#endif  // __CUDACC__
+
 }  // namespace fa

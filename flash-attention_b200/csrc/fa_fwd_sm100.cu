@@ -356,19 +356,52 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     bool ok = true;
     const uint64_t c2 = pack_f2(a.scale_log2, a.scale_log2);
 
-    // dropout bookkeeping: a lane and its partner 8 lanes away own rows r and r + 8 of one 16-row
-    // block, which share every Philox call; each computes half of the calls and they swap halves.
+    // dropout: per-lane generator state (a lane and its partner 8 lanes away own rows r and r + 8 of
+    // one 16-row block, which share every Philox call; each runs half of the calls)
     const int64_t bh_sub =
         (static_cast<int64_t>(b) * a.drop.heads_total + a.drop.head_offset + h) * 256;
     const int L16 = (sq + 15) >> 4;
-    const bool hi_lane = (row & 8) != 0;
-    const uint32_t thr = a.drop.threshold;
-    const uint32_t thr_hi = (thr + 1u) << 16;
-    PhiloxKeys keys;
-    if constexpr (DROPOUT) keys.init(a.drop.key0, a.drop.key1);
+    LanePhilox lp;
+    float thr_term = 0.f;
+    if constexpr (DROPOUT) {
+      lp.init(a.drop, bh_sub, ig);
+      thr_term = fa_keep_thr_term(a.drop.threshold);
+    }
 
     FA_PROF_DECL
     for (int j = 0; j < n && ok; ++j) {
+      const int col0 = kv_tile(j) * kBlockN;
+      int32_t bs_it = 0;
+      if constexpr (BLOCKSPARSE) {
+        const int kb = col0 >> 8;
+        bs_it = (ig >> 4) < a.bs_rows16
+                    ? a.bs_iter[(static_cast<int64_t>(b) * a.bs_kblocks + kb) * a.bs_rows16 + (ig >> 4)]
+                    : -1;
+      }
+      // Dropout: the keep words of the tile (wd[p] covers columns 2p, 2p + 1) do not depend on the
+      // scores, so they are drawn before the wait for S.
+      uint32_t wd[DROPOUT ? 64 : 1];
+      if constexpr (DROPOUT) {
+        // one iteration index per tile: a 128-column tile lies inside one key block
+        int64_t it_index;
+        if constexpr (BLOCKSPARSE) it_index = bs_it;
+        else it_index = fa_iter_index(CAUSAL, col0 >> a.drop.n_shift, ig >> 4, L16, a.drop.n_shift);
+        lp.set_tile(a.drop, it_index, col0);
+        // 16 independent calls (8 column groups x 2 quarters), rounds interleaved so that the
+        // multiply chains of different calls overlap
+        uint32_t st[16][4];
+#pragma unroll
+        for (int grp = 0; grp < 8; ++grp) {
+          lp.start(grp, 0, st[2 * grp]);
+          lp.start(grp, 1, st[2 * grp + 1]);
+        }
+#pragma unroll
+        for (int r = 0; r < 7; ++r)
+#pragma unroll
+          for (int k = 0; k < 16; ++k) lp.round(st[k], r);
+#pragma unroll
+        for (int grp = 0; grp < 8; ++grp) lp.finish(st[2 * grp], st[2 * grp + 1], wd + grp * 8);
+      }
       FA_PROF(0)
       ok = mbar_wait(smem_u32(&sh.s_full[g]), j & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
@@ -385,7 +418,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
       FA_PROF(2)
 
-      const int col0 = kv_tile(j) * kBlockN;
       bool need_mask = (col0 + kBlockN > sk);
       if (CAUSAL) need_mask = need_mask || (col0 + kBlockN - 1 > m0[g]);
       if (need_mask) {
@@ -399,13 +431,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             if (!valid) sr[c][i] = __float_as_uint(-INFINITY);
           }
       }
-      int32_t bs_it = 0;
       if constexpr (BLOCKSPARSE) {
         // a 16-row block that is not in the layout for this 256-column key block sees -inf
-        const int kb = col0 >> 8;
-        bs_it = (ig >> 4) < a.bs_rows16
-                    ? a.bs_iter[(static_cast<int64_t>(b) * a.bs_kblocks + kb) * a.bs_rows16 + (ig >> 4)]
-                    : -1;
         if (bs_it < 0) {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
@@ -446,8 +473,15 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           unpack_f2(fma2(pack_f2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), c2, nmc2), p0, p1);
           unpack_f2(fma2(pack_f2(__uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3])), c2, nmc2), p2, p3);
           p0 = ex2f(p0); p1 = ex2f(p1); p2 = ex2f(p2); p3 = ex2f(p3);
-          sum_a = add2(sum_a, pack_f2(p0, p1));
-          sum_b = add2(sum_b, pack_f2(p2, p3));
+          const uint64_t p01 = pack_f2(p0, p1), p23 = pack_f2(p2, p3);
+          sum_a = add2(sum_a, p01);
+          sum_b = add2(sum_b, p23);
+          if constexpr (DROPOUT) {
+            // the row sum takes the un-dropped p; P*V takes p times the keep factor (1 or 0)
+            const uint32_t w01 = wd[c * 16 + i / 2], w23 = wd[c * 16 + i / 2 + 1];
+            unpack_f2(mul2(p01, pack_f2(fa_keep_factor_lo(w01, thr_term), fa_keep_factor_hi(w01, thr_term))), p0, p1);
+            unpack_f2(mul2(p23, pack_f2(fa_keep_factor_lo(w23, thr_term), fa_keep_factor_hi(w23, thr_term))), p2, p3);
+          }
           pk[c * 16 + i / 2] = pack_lowp<BF16>(p0, p1);
           pk[c * 16 + i / 2 + 1] = pack_lowp<BF16>(p2, p3);
         }
@@ -458,50 +492,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
 
       FA_PROF(5)
-      if constexpr (DROPOUT) {
-        // 16 independent Philox calls (8 column groups x 2 quarters), rounds interleaved so the
-        // multiply chains of different calls overlap.
-        uint32_t st[16][4];
-        const int q0 = hi_lane ? 2 : 0;
-        // one iteration index per tile: a 128-column tile lies inside one key block
-        int64_t it_index;
-        if constexpr (BLOCKSPARSE) it_index = bs_it;
-        else it_index = fa_iter_index(CAUSAL, col0 >> a.drop.n_shift, ig >> 4, L16, a.drop.n_shift);
-#pragma unroll
-        for (int grp = 0; grp < 8; ++grp) {
-          const int jg0 = col0 + grp * 16;
-          fa_philox_init(a.drop, bh_sub, ig, jg0, q0, it_index, st[2 * grp]);
-          fa_philox_init(a.drop, bh_sub, ig, jg0, q0 + 1, it_index, st[2 * grp + 1]);
-        }
-#pragma unroll
-        for (int r = 0; r < 7; ++r)
-#pragma unroll
-          for (int k = 0; k < 16; ++k) philox_round(st[k], keys.k0[r], keys.k1[r]);
-#pragma unroll
-        for (int grp = 0; grp < 8; ++grp) {
-          const uint32_t(&ca)[4] = st[2 * grp];
-          const uint32_t(&cb)[4] = st[2 * grp + 1];
-          // words this row keeps from its own calls / words it hands to the partner row
-          const uint32_t ka0 = hi_lane ? ca[2] : ca[0], ka1 = hi_lane ? ca[3] : ca[1];
-          const uint32_t kb0 = hi_lane ? cb[2] : cb[0], kb1 = hi_lane ? cb[3] : cb[1];
-          const uint32_t ra0 = __shfl_xor_sync(0xffffffffu, hi_lane ? ca[0] : ca[2], 8);
-          const uint32_t ra1 = __shfl_xor_sync(0xffffffffu, hi_lane ? ca[1] : ca[3], 8);
-          const uint32_t rb0 = __shfl_xor_sync(0xffffffffu, hi_lane ? cb[0] : cb[2], 8);
-          const uint32_t rb1 = __shfl_xor_sync(0xffffffffu, hi_lane ? cb[1] : cb[3], 8);
-          // quarter q covers column pairs q (columns 2q, 2q+1) and q + 4 (columns 2q+8, 2q+9)
-          uint32_t* pg = pk + grp * 8;
-          pg[0] &= keep_mask_pair(hi_lane ? ra0 : ka0, thr, thr_hi);
-          pg[4] &= keep_mask_pair(hi_lane ? ra1 : ka1, thr, thr_hi);
-          pg[1] &= keep_mask_pair(hi_lane ? rb0 : kb0, thr, thr_hi);
-          pg[5] &= keep_mask_pair(hi_lane ? rb1 : kb1, thr, thr_hi);
-          pg[2] &= keep_mask_pair(hi_lane ? ka0 : ra0, thr, thr_hi);
-          pg[6] &= keep_mask_pair(hi_lane ? ka1 : ra1, thr, thr_hi);
-          pg[3] &= keep_mask_pair(hi_lane ? kb0 : rb0, thr, thr_hi);
-          pg[7] &= keep_mask_pair(hi_lane ? kb1 : rb1, thr, thr_hi);
-        }
-      }
-
-      FA_PROF(6)
       // P*V of the previous tile must have finished before O is rescaled or its P buffer reused
       if (j > 0) {
         ok = mbar_wait(smem_u32(&sh.o_full[g]), (j - 1) & 1, abort_flag);
