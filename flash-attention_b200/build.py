@@ -44,6 +44,7 @@ def _digest(paths):
             h.update(f.read())
     h.update(" ".join(NVCC_FLAGS).encode())
     h.update(os.environ.get("FA_PROFILE", "").encode())
+    h.update(os.environ.get("FA_DEFS", "").encode())
     return h.hexdigest()
 
 
@@ -61,6 +62,7 @@ def build(force=False, verbose=False):
 
     nvcc = _nvcc()
     extra = ["-DFA_PROFILE"] if os.environ.get("FA_PROFILE") else []
+    extra += os.environ.get("FA_DEFS", "").split()  # extra -D switches of kernel variants
 
     def compile_one(src):
         obj = os.path.join(OBJ_DIR, os.path.basename(src).replace(".cu", ".o"))

@@ -39,9 +39,13 @@ constexpr int kBN = 128;  // key rows per tile
 constexpr int kBwdThreads = 512;
 constexpr int kMaxSparseTiles = 1024;  // query tiles of 128 per sequence in block-sparse mode
 
-template <int D>
+// BS: block-sparse variant (its tile list takes shared memory that the third Q / dO stage would need)
+template <int D, bool BS = false>
 struct BwdCfg {
-  static constexpr int kQStages = (D == 64) ? 2 : 1;
+  // Q / dO ring.  A stage is released when the dK product of its tile has finished and the refill
+  // takes about 1500 clk to land, so with two stages the S / dP products of the next tile start
+  // late and the compute groups wait; the third stage lets the load run a whole tile ahead.
+  static constexpr int kQStages = (D == 64) ? (BS ? 2 : 3) : 1;
   static constexpr bool kAliasDq = (D == 128);  // dQ shares tensor-memory columns with dP
   static constexpr bool kDualIssue = (D == 64);  // second MMA-issuing warp for dV, dK
   static constexpr int kTileBytes = 128 * D * 2;
@@ -55,7 +59,7 @@ struct BwdCfg {
 
 struct BwdShared {
   uint64_t kv_full;
-  uint64_t q_full[2], q_empty[2];
+  uint64_t q_full[3], q_empty[3];
   uint64_t sdp_full, sdp_consumed, pds_ready, pds_free, dq_full, dq_consumed;
   uint64_t dq_group;  // rendezvous of the 128 threads of the dQ group (bounded, unlike bar.sync)
   uint32_t tmem_base;
@@ -89,11 +93,15 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 // accumulates the cycles it spends per phase into status[8..].
 #ifdef FA_PROFILE
 #define FA_PROF_DECL long long prof_t = clock64(); long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+// time stamps (low 32 bits of the SM clock) of one tile's events, for a timeline across the roles
+#define FA_STAMP(tile, idx) if ((tile) >= 5 && (tile) <= 7 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && ka.status) { \
+    ka.status[64 + ((tile) - 5) * 20 + (idx)] = static_cast<int32_t>(clock64()); }
 #define FA_PROF(slot) { const long long now_ = clock64(); prof_acc[slot] += now_ - prof_t; prof_t = now_; }
 #define FA_PROF_FLUSH(base, n) if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && ka.status) { \
     for (int i_ = 0; i_ < 8; ++i_) ka.status[(base) + i_] = static_cast<int32_t>(prof_acc[i_] / ((n) > 0 ? (n) : 1)); }
 #else
 #define FA_PROF_DECL
+#define FA_STAMP(tile, idx)
 #define FA_PROF(slot)
 #define FA_PROF_FLUSH(base, n)
 #endif
@@ -113,7 +121,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
               const __grid_constant__ CUtensorMap tm_dq, const BwdArgs a) {
-  using Cfg = BwdCfg<D>;
+  using Cfg = BwdCfg<D, BLOCKSPARSE>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ BwdShared sh;
 
@@ -199,7 +207,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   if (tid == 0) {
     sh.abort_flag = 0;
     mbar_init(smem_u32(&sh.kv_full), 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 3; ++i) {
       mbar_init(smem_u32(&sh.q_full[i]), 1);
       mbar_init(smem_u32(&sh.q_empty[i]), 1);
     }
@@ -277,6 +285,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (t >= Cfg::kQStages)
           ok = mbar_wait(smem_u32(&sh.q_empty[s]), ((t / Cfg::kQStages) & 1) ^ 1, abort_flag);
         if (!ok) break;
+        FA_STAMP(t - 1, 16)
         const uint32_t bar = smem_u32(&sh.q_full[s]);
         mbar_expect_tx(bar, 2 * Cfg::kTileBytes);
         const int row = q_start + q_tile(t) * kBM;
@@ -303,8 +312,11 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const int sn = (t + 1) % Cfg::kQStages;
         FA_PROF(0)
         if (Cfg::kQStages > 1 && has_next) {
+          FA_STAMP(t, 5)
           ok = mbar_wait(smem_u32(&sh.q_full[sn]), ((t + 1) / Cfg::kQStages) & 1, abort_flag);
+          FA_STAMP(t, 6)
           if (ok) ok = mbar_wait(smem_u32(&sh.sdp_consumed), t & 1, abort_flag);
+          FA_STAMP(t, 7)
           if (!ok) break;
           FA_PROF(1)
           tc_fence_after();
@@ -312,10 +324,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           issue_kk(tDP_, smem_do + sn * Cfg::kTileBytes, smem_v);
           mma_commit(smem_u32(&sh.sdp_full));
           FA_PROF(2)
+          FA_STAMP(t, 8)
         }
         ok = mbar_wait(smem_u32(&sh.pds_ready), t & 1, abort_flag);
         if (!ok) break;
         FA_PROF(3)
+        FA_STAMP(t, 9)
         tc_fence_after();
         if (!Cfg::kAliasDq && t > 0) {
           ok = mbar_wait(smem_u32(&sh.dq_consumed), (t - 1) & 1, abort_flag);
@@ -326,6 +340,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         // dQ first: its tile is read out of tensor memory while dV / dK are still running
         issue_dq(tDQ_, smem_ds, smem_k);
         mma_commit(smem_u32(&sh.dq_full));
+        FA_STAMP(t, 10)
         if (!Cfg::kDualIssue) {
           issue_tt(tDV_, smem_p, smem_do + s * Cfg::kTileBytes, t > 0);
           issue_tt(tDK_, smem_ds, smem_q + s * Cfg::kTileBytes, t > 0);
@@ -359,9 +374,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ok = mbar_wait(smem_u32(&sh.pds_ready), t & 1, abort_flag);
         if (!ok) break;
         FA_PROF(1)
+        FA_STAMP(t, 11)
         tc_fence_after();
         issue_tt(tDV_, smem_p, smem_do + s * Cfg::kTileBytes, t > 0);
+        FA_STAMP(t, 12)
         issue_tt(tDK_, smem_ds, smem_q + s * Cfg::kTileBytes, t > 0);
+        FA_STAMP(t, 13)
         mma_commit(smem_u32(&sh.pds_free));
         mma_commit(smem_u32(&sh.q_empty[s]));
         FA_PROF(2)
@@ -447,10 +465,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
 
       FA_PROF(1)
+      if (w == 0 && row == 0) { FA_STAMP(t, 0) }
       ok = mbar_wait(smem_u32(&sh.sdp_full), t & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       FA_PROF(2)
+      if (w == 0 && row == 0) { FA_STAMP(t, 1) }
       tc_fence_after();
 
       const bool need_mask = (n0 + kBN > sk) || (CAUSAL && (n0 + kBN - 1 > m0));
@@ -468,6 +488,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(smem_u32(&sh.sdp_consumed));
+        if (w == 0 && row == 0) { FA_STAMP(t, 2) }
       }
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -514,6 +535,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           ok = __all_sync(0xffffffffu, ok);
         }
         if (c == 0) { FA_PROF(4) }
+        if (c == 0 && w == 0 && row == 0) { FA_STAMP(t, 3) }
         // 32 16-bit values = 4 chunks of 16 bytes of this row in the 64-column panel w
 #pragma unroll
         for (int ch4 = 0; ch4 < 4; ++ch4) {
@@ -530,6 +552,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       fence_async_smem();
       mbar_arrive(smem_u32(&sh.pds_ready));
       FA_PROF(7)
+      if (w == 0 && row == 0) { FA_STAMP(t, 4) }
     }
     if (w == 0 && row == 0) { FA_PROF_FLUSH(8, nm) }
 
@@ -591,6 +614,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       FA_PROF(1)
+      if (row == 0) { FA_STAMP(t, 14) }
       tc_fence_after();
 #pragma unroll
       for (int half = 0; half < D / 64; ++half) {
@@ -630,6 +654,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
       }
       FA_PROF(2)
+      if (row == 0) { FA_STAMP(t, 15) }
     }
     if (row == 0 && pending) bulk_wait_all();
     if (row == 0) { FA_PROF_FLUSH(32, nm) }
@@ -718,7 +743,7 @@ __global__ void bwd_postprocess_kernel(const BwdArgs a, int dpad) {
 template <int D, bool BF16, bool CAUSAL, bool DROPOUT, bool BS>
 cudaError_t launch_main(const BwdLaunch& l, cudaStream_t stream) {
   auto kernel = fa_bwd_kernel<D, BF16, CAUSAL, DROPOUT, BS>;
-  constexpr int smem = BwdCfg<D>::kSmemBytes;
+  constexpr int smem = BwdCfg<D, BS>::kSmemBytes;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   dim3 grid((l.args.max_seqlen_k + kBN - 1) / kBN, l.args.k.heads, l.args.k.batch);

@@ -19,7 +19,7 @@ def _status_buffer(device):
     """Per-device int32[4] the kernels write to when they abandon a bounded wait."""
     buf = _status.get(device)
     if buf is None:
-        buf = torch.zeros(64, dtype=torch.int32, device=device)
+        buf = torch.zeros(128, dtype=torch.int32, device=device)
         _status[device] = buf
     return buf
 
