@@ -47,6 +47,12 @@ struct BwdCfg {
   // late and the compute groups wait; the third stage lets the load run a whole tile ahead.
   static constexpr int kQStages = (D == 64) ? (BS ? 2 : 3) : 1;
   static constexpr bool kAliasDq = (D == 128);  // dQ shares tensor-memory columns with dP
+  // d = 128 has room for a single Q / dO stage, and its 64 KB refill takes about 3000 clk (one
+  // 128-byte row per ~5 clk), all of it on the critical path between two tiles.  So Q and dO are
+  // released and refilled separately: dK (the last reader of Q) is issued first and Q refilled
+  // behind it, then dV and dO, then dQ; S of the next tile starts when Q has landed, while dO is
+  // still on its way.
+  static constexpr bool kSplitLoads = (kQStages == 1);
   static constexpr bool kDualIssue = (D == 64);  // second MMA-issuing warp for dV, dK
   static constexpr int kTileBytes = 128 * D * 2;
   static constexpr int kPdsBytes = 128 * 128 * 2;
@@ -60,6 +66,7 @@ struct BwdCfg {
 struct BwdShared {
   uint64_t kv_full;
   uint64_t q_full[3], q_empty[3];
+  uint64_t do_full, do_empty;  // dO when it is loaded apart from Q (kSplitLoads)
   uint64_t sdp_full, sdp_consumed, pds_ready, pds_free, dq_full, dq_consumed;
   uint64_t dq_group;  // rendezvous of the 128 threads of the dQ group (bounded, unlike bar.sync)
   uint32_t tmem_base;
@@ -211,6 +218,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       mbar_init(smem_u32(&sh.q_full[i]), 1);
       mbar_init(smem_u32(&sh.q_empty[i]), 1);
     }
+    mbar_init(smem_u32(&sh.do_full), 1);
+    mbar_init(smem_u32(&sh.do_empty), 1);
     mbar_init(smem_u32(&sh.sdp_full), 1);
     mbar_init(smem_u32(&sh.sdp_consumed), 2 * kBM);
     mbar_init(smem_u32(&sh.pds_ready), 2 * kBM);
@@ -286,12 +295,23 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           ok = mbar_wait(smem_u32(&sh.q_empty[s]), ((t / Cfg::kQStages) & 1) ^ 1, abort_flag);
         if (!ok) break;
         FA_STAMP(t - 1, 16)
-        const uint32_t bar = smem_u32(&sh.q_full[s]);
-        mbar_expect_tx(bar, 2 * Cfg::kTileBytes);
         const int row = q_start + q_tile(t) * kBM;
-        for (int p = 0; p < D / 64; ++p) {
-          tma_load_3d(smem_q + s * Cfg::kTileBytes + p * 16384, &tm_q, bar, p * 64, row, h);
-          tma_load_3d(smem_do + s * Cfg::kTileBytes + p * 16384, &tm_do, bar, p * 64, row, h);
+        if constexpr (Cfg::kSplitLoads) {
+          const uint32_t bar = smem_u32(&sh.q_full[0]);
+          mbar_expect_tx(bar, Cfg::kTileBytes);
+          for (int p = 0; p < D / 64; ++p) tma_load_3d(smem_q + p * 16384, &tm_q, bar, p * 64, row, h);
+          if (t >= 1) ok = mbar_wait(smem_u32(&sh.do_empty), (t & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          const uint32_t bar_do = smem_u32(&sh.do_full);
+          mbar_expect_tx(bar_do, Cfg::kTileBytes);
+          for (int p = 0; p < D / 64; ++p) tma_load_3d(smem_do + p * 16384, &tm_do, bar_do, p * 64, row, h);
+        } else {
+          const uint32_t bar = smem_u32(&sh.q_full[s]);
+          mbar_expect_tx(bar, 2 * Cfg::kTileBytes);
+          for (int p = 0; p < D / 64; ++p) {
+            tma_load_3d(smem_q + s * Cfg::kTileBytes + p * 16384, &tm_q, bar, p * 64, row, h);
+            tma_load_3d(smem_do + s * Cfg::kTileBytes + p * 16384, &tm_do, bar, p * 64, row, h);
+          }
         }
       }
     } else if (warp == 13 && lane == 0) {
@@ -302,6 +322,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (ok) {
         tc_fence_after();
         issue_kk(tS_, smem_q, smem_k);
+        if constexpr (Cfg::kSplitLoads) {
+          ok = mbar_wait(smem_u32(&sh.do_full), 0, abort_flag);
+          tc_fence_after();
+        }
+      }
+      if (ok) {
         issue_kk(tDP_, smem_do, smem_v);
         mma_commit(smem_u32(&sh.sdp_full));
       }
@@ -337,29 +363,51 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           tc_fence_after();
         }
         FA_PROF(4)
-        // dQ first: its tile is read out of tensor memory while dV / dK are still running
-        issue_dq(tDQ_, smem_ds, smem_k);
-        mma_commit(smem_u32(&sh.dq_full));
-        FA_STAMP(t, 10)
-        if (!Cfg::kDualIssue) {
-          issue_tt(tDV_, smem_p, smem_do + s * Cfg::kTileBytes, t > 0);
-          issue_tt(tDK_, smem_ds, smem_q + s * Cfg::kTileBytes, t > 0);
+        if constexpr (Cfg::kSplitLoads) {
+          // dK, dV, dQ in the order that frees Q, then dO, as early as possible
+          issue_tt(tDK_, smem_ds, smem_q, t > 0);
+          mma_commit(smem_u32(&sh.q_empty[0]));
+          issue_tt(tDV_, smem_p, smem_do, t > 0);
+          mma_commit(smem_u32(&sh.do_empty));
+          issue_dq(tDQ_, smem_ds, smem_k);
+          mma_commit(smem_u32(&sh.dq_full));
+          FA_STAMP(t, 10)
+          mma_commit(smem_u32(&sh.pds_free));
+        } else {
+          // dQ first: its tile is read out of tensor memory while dV / dK are still running
+          issue_dq(tDQ_, smem_ds, smem_k);
+          mma_commit(smem_u32(&sh.dq_full));
+          FA_STAMP(t, 10)
+          if (!Cfg::kDualIssue) {
+            issue_tt(tDV_, smem_p, smem_do + s * Cfg::kTileBytes, t > 0);
+            issue_tt(tDK_, smem_ds, smem_q + s * Cfg::kTileBytes, t > 0);
+          }
+          mma_commit(smem_u32(&sh.pds_free));
+          if (!Cfg::kDualIssue) mma_commit(smem_u32(&sh.q_empty[s]));
         }
-        mma_commit(smem_u32(&sh.pds_free));
-        if (!Cfg::kDualIssue) mma_commit(smem_u32(&sh.q_empty[s]));
         FA_PROF(5)
         if (Cfg::kQStages == 1 && has_next) {
+          FA_STAMP(t, 5)
           ok = mbar_wait(smem_u32(&sh.q_full[0]), (t + 1) & 1, abort_flag);
           if (!ok) break;
+          FA_STAMP(t, 6)
           tc_fence_after();
           issue_kk(tS_, smem_q, smem_k);
+          FA_STAMP(t, 12)
+          if constexpr (Cfg::kSplitLoads) {
+            ok = mbar_wait(smem_u32(&sh.do_full), (t + 1) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+          }
           if (Cfg::kAliasDq) {
             ok = mbar_wait(smem_u32(&sh.dq_consumed), t & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
           }
+          FA_STAMP(t, 7)
           issue_kk(tDP_, smem_do, smem_v);
           mma_commit(smem_u32(&sh.sdp_full));
+          FA_STAMP(t, 8)
           FA_PROF(6)
         }
       }
@@ -616,6 +664,43 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       FA_PROF(1)
       if (row == 0) { FA_STAMP(t, 14) }
       tc_fence_after();
+      if constexpr (Cfg::kAliasDq) {
+        // dQ shares its columns with the next dP, so the columns are released as early as possible:
+        // both boxes of a 64-column half go to registers before anything waits for the staging
+        // buffer, and the release follows the loads of the second half.
+#pragma unroll
+        for (int half = 0; half < D / 64; ++half) {
+          uint32_t r0[32], r1[32];
+          tmem_ld32(tDQ + half * 64, r0);
+          tmem_ld32(tDQ + half * 64 + 32, r1);
+          tmem_wait_ld();
+          if (half == D / 64 - 1) {
+            tc_fence_before();
+            mbar_arrive(smem_u32(&sh.dq_consumed));
+          }
+          // the staging buffer is free once the previous reduce has read it
+          if (row == 0 && pending) bulk_wait_read();
+          ok = group_sync();
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            const uint32_t off = row * 128 + ((ch ^ (row & 7)) << 4);
+            *reinterpret_cast<uint4*>(dq_stage + off) = make_uint4(r0[4 * ch], r0[4 * ch + 1], r0[4 * ch + 2], r0[4 * ch + 3]);
+            *reinterpret_cast<uint4*>(dq_stage + 16384 + off) = make_uint4(r1[4 * ch], r1[4 * ch + 1], r1[4 * ch + 2], r1[4 * ch + 3]);
+          }
+          fence_async_smem();
+          ok = group_sync();
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          if (row == 0) {
+            tma_reduce_add_3d(&tm_dq, stage_addr, half * 64, q_start + m0, h);
+            tma_reduce_add_3d(&tm_dq, stage_addr + 16384, half * 64 + 32, q_start + m0, h);
+            bulk_commit();
+            pending = true;
+          }
+        }
+      } else {
 #pragma unroll
       for (int half = 0; half < D / 64; ++half) {
 #pragma unroll
@@ -652,6 +737,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           bulk_commit();
           pending = true;
         }
+      }
       }
       FA_PROF(2)
       if (row == 0) { FA_STAMP(t, 15) }
