@@ -42,18 +42,17 @@ constexpr int kMaxSparseTiles = 1024;  // query tiles of 128 per sequence in blo
 // BS: block-sparse variant (its tile list takes shared memory that the third Q / dO stage would need)
 template <int D, bool BS = false>
 struct BwdCfg {
-  // Q / dO ring.  A stage is released when the dK product of its tile has finished and the refill
-  // takes about 1500 clk to land, so with two stages the S / dP products of the next tile start
-  // late and the compute groups wait; the third stage lets the load run a whole tile ahead.
+  // d = 128 runs a different schedule: shared memory holds a single stage of Q and of dO, each
+  // with its own barriers, and the compute groups work in two phases (P~ from S, then dS from dP)
+  // so that dV can be issued - and dO released for its refill - before dP is even needed.
+  static constexpr bool kTwoPhase = (D == 128);
+  // Q / dO ring.  d = 64: a stage is released when the dK product of its tile has finished and
+  // the refill takes about 1500 clk to land, so with two stages the S / dP products of the next
+  // tile start late and the compute groups wait; the third stage lets the load run a whole tile
+  // ahead.
   static constexpr int kQStages = (D == 64) ? (BS ? 2 : 3) : 1;
-  static constexpr bool kAliasDq = (D == 128);  // dQ shares tensor-memory columns with dP
-  // d = 128 has room for a single Q / dO stage, and its 64 KB refill takes about 3000 clk (one
-  // 128-byte row per ~5 clk), all of it on the critical path between two tiles.  So Q and dO are
-  // released and refilled separately: dK (the last reader of Q) is issued first and Q refilled
-  // behind it, then dV and dO, then dQ; S of the next tile starts when Q has landed, while dO is
-  // still on its way.
-  static constexpr bool kSplitLoads = (kQStages == 1);
-  static constexpr bool kDualIssue = (D == 64);  // second MMA-issuing warp for dV, dK
+  static constexpr bool kAliasDq = kTwoPhase;     // dQ shares tensor-memory columns with dP
+  static constexpr bool kDualIssue = !kTwoPhase;  // second MMA-issuing warp for dV, dK
   static constexpr int kTileBytes = 128 * D * 2;
   static constexpr int kPdsBytes = 128 * 128 * 2;
   static constexpr int kDqStageBytes = 2 * 16384;  // two [128 rows x 32 fp32] boxes
@@ -66,8 +65,13 @@ struct BwdCfg {
 struct BwdShared {
   uint64_t kv_full;
   uint64_t q_full[3], q_empty[3];
-  uint64_t do_full, do_empty;  // dO when it is loaded apart from Q (kSplitLoads)
+  uint64_t do_full, do_empty;  // dO ring of the two-phase schedule (one stage)
+  // d = 64: S and dP together / P~ and dS together.  Two-phase schedule: sdp_full = dP landed,
+  // sdp_consumed = S read into registers, pds_ready = dS stored, pds_free = dV has read P~.
   uint64_t sdp_full, sdp_consumed, pds_ready, pds_free, dq_full, dq_consumed;
+  uint64_t s_full;    // two-phase: S landed
+  uint64_t p_ready;   // two-phase: P~ stored
+  uint64_t ds_free;   // two-phase: dK and dQ have finished reading the dS buffer
   uint64_t dq_group;  // rendezvous of the 128 threads of the dQ group (bounded, unlike bar.sync)
   uint32_t tmem_base;
   int abort_flag;
@@ -227,6 +231,9 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     mbar_init(smem_u32(&sh.dq_full), 1);
     mbar_init(smem_u32(&sh.dq_consumed), kBM);
     mbar_init(smem_u32(&sh.dq_group), kBM);
+    mbar_init(smem_u32(&sh.s_full), 1);
+    mbar_init(smem_u32(&sh.p_ready), 2 * kBM);
+    mbar_init(smem_u32(&sh.ds_free), 1);
     fence_mbar_init();
   }
   if (warp == 12) tmem_alloc(smem_u32(&sh.tmem_base), 512);
@@ -291,20 +298,24 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       bool ok = true;
       for (int t = 0; t < nm && ok; ++t) {
         const int s = t % Cfg::kQStages;
-        if (t >= Cfg::kQStages)
+        if (!Cfg::kTwoPhase && t >= Cfg::kQStages)
           ok = mbar_wait(smem_u32(&sh.q_empty[s]), ((t / Cfg::kQStages) & 1) ^ 1, abort_flag);
         if (!ok) break;
-        FA_STAMP(t - 1, 16)
+        if (!Cfg::kTwoPhase) { FA_STAMP(t - 1, 16) }
         const int row = q_start + q_tile(t) * kBM;
-        if constexpr (Cfg::kSplitLoads) {
-          const uint32_t bar = smem_u32(&sh.q_full[0]);
-          mbar_expect_tx(bar, Cfg::kTileBytes);
-          for (int p = 0; p < D / 64; ++p) tma_load_3d(smem_q + p * 16384, &tm_q, bar, p * 64, row, h);
+        if constexpr (Cfg::kTwoPhase) {
+          // dO(t) follows dV(t - 1), Q(t) follows dK(t - 1): the order in which they finish
           if (t >= 1) ok = mbar_wait(smem_u32(&sh.do_empty), (t & 1) ^ 1, abort_flag);
           if (!ok) break;
           const uint32_t bar_do = smem_u32(&sh.do_full);
           mbar_expect_tx(bar_do, Cfg::kTileBytes);
           for (int p = 0; p < D / 64; ++p) tma_load_3d(smem_do + p * 16384, &tm_do, bar_do, p * 64, row, h);
+          if (t >= 1) ok = mbar_wait(smem_u32(&sh.q_empty[0]), (t & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          FA_STAMP(t - 1, 16)
+          const uint32_t bar = smem_u32(&sh.q_full[0]);
+          mbar_expect_tx(bar, Cfg::kTileBytes);
+          for (int p = 0; p < D / 64; ++p) tma_load_3d(smem_q + p * 16384, &tm_q, bar, p * 64, row, h);
         } else {
           const uint32_t bar = smem_u32(&sh.q_full[s]);
           mbar_expect_tx(bar, 2 * Cfg::kTileBytes);
@@ -316,102 +327,121 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
     } else if (warp == 13 && lane == 0) {
       // -------------------------------------------------------------- MMA issuer 1
-      // d = 64: S, dP and dQ (dV, dK go through issuer 2).  d = 128: every product, in order.
       bool ok = mbar_wait(smem_u32(&sh.kv_full), 0, abort_flag);
       if (ok) ok = mbar_wait(smem_u32(&sh.q_full[0]), 0, abort_flag);
-      if (ok) {
-        tc_fence_after();
-        issue_kk(tS_, smem_q, smem_k);
-        if constexpr (Cfg::kSplitLoads) {
-          ok = mbar_wait(smem_u32(&sh.do_full), 0, abort_flag);
+      if constexpr (Cfg::kTwoPhase) {
+        // d = 128: every product, issued by this thread in the order
+        //   dV(t) | dK(t), dQ(t) | S(t+1) | dP(t+1)
+        // dV(t) follows P~ (end of phase one of the compute groups) and releases dO for its
+        // refill while phase two is still running.  dK, dQ follow dS; dK releases Q.  S(t+1) is
+        // issued when Q has landed, dP(t+1) when dO has landed and the dQ group has read dQ(t)
+        // out of the columns it shares with dP.
+        if (ok) {
           tc_fence_after();
+          issue_kk(tS_, smem_q, smem_k);
+          mma_commit(smem_u32(&sh.s_full));
+          ok = mbar_wait(smem_u32(&sh.do_full), 0, abort_flag);
         }
-      }
-      if (ok) {
-        issue_kk(tDP_, smem_do, smem_v);
-        mma_commit(smem_u32(&sh.sdp_full));
-      }
-      FA_PROF_DECL
-      for (int t = 0; t < nm && ok; ++t) {
-        const int s = t % Cfg::kQStages;
-        const bool has_next = t + 1 < nm;
-        const int sn = (t + 1) % Cfg::kQStages;
-        FA_PROF(0)
-        if (Cfg::kQStages > 1 && has_next) {
-          FA_STAMP(t, 5)
-          ok = mbar_wait(smem_u32(&sh.q_full[sn]), ((t + 1) / Cfg::kQStages) & 1, abort_flag);
-          FA_STAMP(t, 6)
-          if (ok) ok = mbar_wait(smem_u32(&sh.sdp_consumed), t & 1, abort_flag);
-          FA_STAMP(t, 7)
+        if (ok) {
+          tc_fence_after();
+          issue_kk(tDP_, smem_do, smem_v);
+          mma_commit(smem_u32(&sh.sdp_full));
+        }
+        FA_PROF_DECL
+        for (int t = 0; t < nm && ok; ++t) {
+          const bool has_next = t + 1 < nm;
+          FA_PROF(0)
+          ok = mbar_wait(smem_u32(&sh.p_ready), t & 1, abort_flag);
           if (!ok) break;
           FA_PROF(1)
           tc_fence_after();
-          issue_kk(tS_, smem_q + sn * Cfg::kTileBytes, smem_k);
-          issue_kk(tDP_, smem_do + sn * Cfg::kTileBytes, smem_v);
-          mma_commit(smem_u32(&sh.sdp_full));
-          FA_PROF(2)
-          FA_STAMP(t, 8)
-        }
-        ok = mbar_wait(smem_u32(&sh.pds_ready), t & 1, abort_flag);
-        if (!ok) break;
-        FA_PROF(3)
-        FA_STAMP(t, 9)
-        tc_fence_after();
-        if (!Cfg::kAliasDq && t > 0) {
-          ok = mbar_wait(smem_u32(&sh.dq_consumed), (t - 1) & 1, abort_flag);
+          issue_tt(tDV_, smem_p, smem_do, t > 0);
+          mma_commit(smem_u32(&sh.pds_free));
+          mma_commit(smem_u32(&sh.do_empty));
+          FA_STAMP(t, 11)
+          ok = mbar_wait(smem_u32(&sh.pds_ready), t & 1, abort_flag);
           if (!ok) break;
+          FA_PROF(2)
+          FA_STAMP(t, 9)
           tc_fence_after();
-        }
-        FA_PROF(4)
-        if constexpr (Cfg::kSplitLoads) {
-          // dK, dV, dQ in the order that frees Q, then dO, as early as possible
           issue_tt(tDK_, smem_ds, smem_q, t > 0);
           mma_commit(smem_u32(&sh.q_empty[0]));
-          issue_tt(tDV_, smem_p, smem_do, t > 0);
-          mma_commit(smem_u32(&sh.do_empty));
           issue_dq(tDQ_, smem_ds, smem_k);
           mma_commit(smem_u32(&sh.dq_full));
+          mma_commit(smem_u32(&sh.ds_free));
           FA_STAMP(t, 10)
-          mma_commit(smem_u32(&sh.pds_free));
-        } else {
-          // dQ first: its tile is read out of tensor memory while dV / dK are still running
-          issue_dq(tDQ_, smem_ds, smem_k);
-          mma_commit(smem_u32(&sh.dq_full));
-          FA_STAMP(t, 10)
-          if (!Cfg::kDualIssue) {
-            issue_tt(tDV_, smem_p, smem_do + s * Cfg::kTileBytes, t > 0);
-            issue_tt(tDK_, smem_ds, smem_q + s * Cfg::kTileBytes, t > 0);
+          FA_PROF(3)
+          if (has_next) {
+            FA_STAMP(t, 5)
+            ok = mbar_wait(smem_u32(&sh.q_full[0]), (t + 1) & 1, abort_flag);
+            FA_STAMP(t, 6)
+            if (ok) ok = mbar_wait(smem_u32(&sh.sdp_consumed), t & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            issue_kk(tS_, smem_q, smem_k);
+            mma_commit(smem_u32(&sh.s_full));
+            FA_STAMP(t, 12)
+            FA_PROF(4)
+            ok = mbar_wait(smem_u32(&sh.do_full), (t + 1) & 1, abort_flag);
+            if (ok) ok = mbar_wait(smem_u32(&sh.dq_consumed), t & 1, abort_flag);
+            if (!ok) break;
+            FA_STAMP(t, 7)
+            tc_fence_after();
+            issue_kk(tDP_, smem_do, smem_v);
+            mma_commit(smem_u32(&sh.sdp_full));
+            FA_STAMP(t, 8)
+            FA_PROF(5)
           }
-          mma_commit(smem_u32(&sh.pds_free));
-          if (!Cfg::kDualIssue) mma_commit(smem_u32(&sh.q_empty[s]));
         }
-        FA_PROF(5)
-        if (Cfg::kQStages == 1 && has_next) {
-          FA_STAMP(t, 5)
-          ok = mbar_wait(smem_u32(&sh.q_full[0]), (t + 1) & 1, abort_flag);
-          if (!ok) break;
-          FA_STAMP(t, 6)
+        FA_PROF_FLUSH(16, nm)
+      } else {
+        // d = 64: S, dP and dQ (dV, dK go through issuer 2)
+        if (ok) {
           tc_fence_after();
           issue_kk(tS_, smem_q, smem_k);
-          FA_STAMP(t, 12)
-          if constexpr (Cfg::kSplitLoads) {
-            ok = mbar_wait(smem_u32(&sh.do_full), (t + 1) & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-          }
-          if (Cfg::kAliasDq) {
-            ok = mbar_wait(smem_u32(&sh.dq_consumed), t & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-          }
-          FA_STAMP(t, 7)
           issue_kk(tDP_, smem_do, smem_v);
           mma_commit(smem_u32(&sh.sdp_full));
-          FA_STAMP(t, 8)
-          FA_PROF(6)
         }
+        FA_PROF_DECL
+        for (int t = 0; t < nm && ok; ++t) {
+          const bool has_next = t + 1 < nm;
+          const int sn = (t + 1) % Cfg::kQStages;
+          FA_PROF(0)
+          if (has_next) {
+            FA_STAMP(t, 5)
+            ok = mbar_wait(smem_u32(&sh.q_full[sn]), ((t + 1) / Cfg::kQStages) & 1, abort_flag);
+            FA_STAMP(t, 6)
+            if (ok) ok = mbar_wait(smem_u32(&sh.sdp_consumed), t & 1, abort_flag);
+            FA_STAMP(t, 7)
+            if (!ok) break;
+            FA_PROF(1)
+            tc_fence_after();
+            issue_kk(tS_, smem_q + sn * Cfg::kTileBytes, smem_k);
+            issue_kk(tDP_, smem_do + sn * Cfg::kTileBytes, smem_v);
+            mma_commit(smem_u32(&sh.sdp_full));
+            FA_PROF(2)
+            FA_STAMP(t, 8)
+          }
+          ok = mbar_wait(smem_u32(&sh.pds_ready), t & 1, abort_flag);
+          if (!ok) break;
+          FA_PROF(3)
+          FA_STAMP(t, 9)
+          tc_fence_after();
+          if (t > 0) {
+            ok = mbar_wait(smem_u32(&sh.dq_consumed), (t - 1) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          FA_PROF(4)
+          // its tile is read out of tensor memory while dV / dK are still running
+          issue_dq(tDQ_, smem_ds, smem_k);
+          mma_commit(smem_u32(&sh.dq_full));
+          FA_STAMP(t, 10)
+          mma_commit(smem_u32(&sh.pds_free));
+          FA_PROF(5)
+        }
+        FA_PROF_FLUSH(16, nm)
       }
-      FA_PROF_FLUSH(16, nm)
     } else if (warp == 14 && lane == 0 && Cfg::kDualIssue) {
       // -------------------------------------------------------------- MMA issuer 2: dV, dK
       bool ok = true;
@@ -512,6 +542,112 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         for (int g4 = 0; g4 < 4; ++g4) lp.finish(st[2 * g4], st[2 * g4 + 1], wd + g4 * 8);
       }
 
+      const bool need_mask = (n0 + kBN > sk) || (CAUSAL && (n0 + kBN - 1 > m0));
+      if constexpr (Cfg::kTwoPhase) {
+        // ---- phase one: P from S.  P~ goes to shared memory (dV can start), P stays in registers.
+        FA_PROF(1)
+        if (w == 0 && row == 0) { FA_STAMP(t, 0) }
+        ok = mbar_wait(smem_u32(&sh.s_full), t & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        FA_PROF(2)
+        if (w == 0 && row == 0) { FA_STAMP(t, 1) }
+        tc_fence_after();
+        uint32_t pf[2][32];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t sr[32];
+          tmem_ld32(tS + c * 32, sr);
+          tmem_wait_ld();
+          if (c == 1) {
+            tc_fence_before();
+            mbar_arrive(smem_u32(&sh.sdp_consumed));
+            if (w == 0 && row == 0) { FA_STAMP(t, 2) }
+          }
+          uint32_t pp[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0, p1;
+            unpack_f2(fma2(pack_f2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), c2, nlse2), p0, p1);
+            p0 = ex2f(p0);
+            p1 = ex2f(p1);
+            if (need_mask) {
+              const int col = cbase + c * 32 + i;
+              bool v0 = col < sk, v1 = col + 1 < sk;
+              if (CAUSAL) { v0 = v0 && (col <= ig); v1 = v1 && (col + 1 <= ig); }
+              if (!v0) p0 = 0.f;
+              if (!v1) p1 = 0.f;
+            }
+            if (BLOCKSPARSE && !row_in_layout) { p0 = 0.f; p1 = 0.f; }
+            pf[c][i] = __float_as_uint(p0);
+            pf[c][i + 1] = __float_as_uint(p1);
+            float k0 = p0, k1 = p1;
+            if constexpr (DROPOUT) {
+              const uint32_t word = wd[c * 16 + (i >> 1)];
+              unpack_f2(mul2(pack_f2(p0, p1),
+                             pack_f2(fa_keep_factor_lo(word, thr_term), fa_keep_factor_hi(word, thr_term))), k0, k1);
+            }
+            pp[i >> 1] = pack_lowp<BF16>(k0, k1);
+          }
+          // dV of the previous tile must have finished reading the P~ buffer
+          if (c == 0 && t > 0) {
+            ok = mbar_wait(smem_u32(&sh.pds_free), (t - 1) & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+          }
+#pragma unroll
+          for (int ch4 = 0; ch4 < 4; ++ch4) {
+            const int ch = c * 4 + ch4;
+            const uint32_t off = w * 16384 + row * 128 + ((ch ^ (row & 7)) << 4);
+            *reinterpret_cast<uint4*>(p_ptr + off) =
+                make_uint4(pp[4 * ch4], pp[4 * ch4 + 1], pp[4 * ch4 + 2], pp[4 * ch4 + 3]);
+          }
+        }
+        if (!ok) break;
+        fence_async_smem();
+        mbar_arrive(smem_u32(&sh.p_ready));
+        FA_PROF(3)
+        if (w == 0 && row == 0) { FA_STAMP(t, 3) }
+
+        // ---- phase two: dS = P~ * dP - P * D from dP
+        ok = mbar_wait(smem_u32(&sh.sdp_full), t & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        FA_PROF(4)
+        if (w == 0 && row == 0) { FA_STAMP(t, 13) }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t dr[32];
+          tmem_ld32(tDP + c * 32, dr);
+          tmem_wait_ld();
+          uint32_t pds[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const uint64_t p01 = pack_f2(__uint_as_float(pf[c][i]), __uint_as_float(pf[c][i + 1]));
+            uint64_t k01 = p01;
+            if constexpr (DROPOUT) {
+              const uint32_t word = wd[c * 16 + (i >> 1)];
+              k01 = mul2(p01, pack_f2(fa_keep_factor_lo(word, thr_term), fa_keep_factor_hi(word, thr_term)));
+            }
+            float s0, s1;
+            unpack_f2(fma2(k01, pack_f2(__uint_as_float(dr[i]), __uint_as_float(dr[i + 1])), mul2(p01, nd2)), s0, s1);
+            pds[i >> 1] = pack_lowp<BF16>(s0, s1);
+          }
+          // dK, dQ of the previous tile must have finished reading the dS buffer
+          if (c == 0 && t > 0) {
+            ok = mbar_wait(smem_u32(&sh.ds_free), (t - 1) & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+          }
+#pragma unroll
+          for (int ch4 = 0; ch4 < 4; ++ch4) {
+            const int ch = c * 4 + ch4;
+            const uint32_t off = w * 16384 + row * 128 + ((ch ^ (row & 7)) << 4);
+            *reinterpret_cast<uint4*>(ds_ptr + off) =
+                make_uint4(pds[4 * ch4], pds[4 * ch4 + 1], pds[4 * ch4 + 2], pds[4 * ch4 + 3]);
+          }
+        }
+        tc_fence_before();  // the dP columns are about to be overwritten by dQ
+      } else {
       FA_PROF(1)
       if (w == 0 && row == 0) { FA_STAMP(t, 0) }
       ok = mbar_wait(smem_u32(&sh.sdp_full), t & 1, abort_flag);
@@ -521,7 +657,6 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (w == 0 && row == 0) { FA_STAMP(t, 1) }
       tc_fence_after();
 
-      const bool need_mask = (n0 + kBN > sk) || (CAUSAL && (n0 + kBN - 1 > m0));
       // This thread's 64 scores and 64 dP values go to registers at once, so that the next tile's
       // S and dP products can overwrite tensor memory while this tile is still being processed.
       // (d = 64 only: at d = 128 the next dP waits for the dQ read-out anyway, and the registers
@@ -595,6 +730,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               make_uint4(pds[4 * ch4], pds[4 * ch4 + 1], pds[4 * ch4 + 2], pds[4 * ch4 + 3]);
         }
       }
+      }
       if (!ok) break;
       FA_PROF(6)
       fence_async_smem();
@@ -607,6 +743,9 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     // ---------------- epilogue: group 0 writes dV = acc / p_keep, group 1 writes dK = acc * scale / p_keep
     if (ok) {
       ok = mbar_wait(smem_u32(&sh.pds_free), (nm - 1) & 1, abort_flag);
+      if constexpr (Cfg::kTwoPhase) {
+        if (ok) ok = mbar_wait(smem_u32(&sh.ds_free), (nm - 1) & 1, abort_flag);
+      }
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
@@ -700,6 +839,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             pending = true;
           }
         }
+
       } else {
 #pragma unroll
       for (int half = 0; half < D / 64; ++half) {
