@@ -58,7 +58,11 @@ int make_tile_map(CUtensorMap* tm, const void* base, bool bf16, int64_t rows, in
   if (!enc) return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   // A thread that has only used the runtime API lazily (an autograd worker, for instance) may not
   // have the primary context bound yet; the driver call below needs it.
-  FA_CUDA(cudaFree(nullptr));
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    FA_CUDA(cudaFree(nullptr));
+    context_bound = true;
+  }
   FA_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "tensor base must be 16-byte aligned");
   FA_REQUIRE((row_stride * 2) % 16 == 0 && (head_stride * 2) % 16 == 0,
              "row and head strides must be multiples of 8 elements");

@@ -9,7 +9,7 @@
 //      P = exp2(scale*log2e*S - LSE*log2e), regenerates the dropout mask, forms
 //      dS = P*(dP - D) (kept) or -P*D (dropped), writes the 16-bit P~ and dS to shared memory
 //      and issues dV += P~^T dO, dK += dS^T Q, dQ = dS K.  dQ tiles are added into the fp32
-//      accumulator with vector reductions; dK and dV stay in tensor memory until the end.
+//      accumulator with TMA reduce-adds; dK and dV stay in tensor memory until the end.
 //   3. bwd_postprocess: dq = accumulator * scale / p_keep in the 16-bit output type.
 //
 // The formulas are those of the reference backward
@@ -24,6 +24,14 @@
 //   warps 8-11  dQ group: tensor memory -> global reductions
 //   warp 12     TMA producer     warp 13  MMA issuer (S, dP, dQ; everything at d = 128)
 //   warp 14     second MMA issuer (dV, dK) at d = 64      warp 15 idle
+//
+// Schedules.  d = 64: Q and dO travel together through a three-stage ring; S and dP of tile t + 1
+// are issued as soon as the compute groups have read tile t into registers.  d = 128: shared
+// memory holds one stage of Q and one of dO, each with its own barriers.  The compute groups work
+// in two phases, P~ from S and then dS from dP; dV(t) is issued after phase one and releases dO
+// for its refill, dK(t) and dQ(t) follow phase two and dK releases Q; S(t + 1) is issued when Q
+// has landed and dP(t + 1) when dO has landed and the dQ group has read dQ(t) out of the
+// tensor-memory columns it shares with dP.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "fa_kernels.h"
@@ -970,7 +978,8 @@ template <int D, bool BF16, bool CAUSAL, bool DROPOUT, bool BS>
 cudaError_t launch_main(const BwdLaunch& l, cudaStream_t stream) {
   auto kernel = fa_bwd_kernel<D, BF16, CAUSAL, DROPOUT, BS>;
   constexpr int smem = BwdCfg<D, BS>::kSmemBytes;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static SmemLimitFlags smem_limit_set;  // one per template instantiation of this function
+  cudaError_t e = set_smem_limit_once(kernel, smem, smem_limit_set);
   if (e != cudaSuccess) return e;
   dim3 grid((l.args.max_seqlen_k + kBN - 1) / kBN, l.args.k.heads, l.args.k.batch);
   kernel<<<grid, kBwdThreads, smem, stream>>>(l.tm_q, l.tm_k, l.tm_v, l.tm_do, l.tm_dq, l.args);

@@ -583,7 +583,8 @@ template <int D, bool BF16, bool CAUSAL, bool DROPOUT, bool BS>
 cudaError_t launch_one(const FwdLaunch& l, cudaStream_t stream) {
   auto kernel = fa_fwd_kernel<D, BF16, CAUSAL, DROPOUT, BS>;
   constexpr int smem = FwdCfg<D>::kSmemBytes;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static SmemLimitFlags smem_limit_set;  // one per template instantiation of this function
+  cudaError_t e = set_smem_limit_once(kernel, smem, smem_limit_set);
   if (e != cudaSuccess) return e;
   dim3 grid((l.max_seqlen_q + 2 * kBlockM - 1) / (2 * kBlockM), l.args.heads, l.args.batch);
   kernel<<<grid, kFwdThreads, smem, stream>>>(l.tm_q, l.tm_k, l.tm_v, l.args);

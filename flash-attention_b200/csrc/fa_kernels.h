@@ -1,5 +1,6 @@
 // Host-side launch interface between the C ABI (fa_api.cu) and the kernel translation units.
 #pragma once
+#include <atomic>
 #include <cstdint>
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -72,5 +73,22 @@ cudaError_t launch_bs_table(int32_t* table, const int32_t* blockmask, const int3
 cudaError_t launch_dropout_mask(uint8_t* out, int b, int h, const DropoutParams& dp, bool causal,
                                 int sq, int sk, const int32_t* bs_iter, int bs_kblocks,
                                 int bs_rows16, cudaStream_t stream);
+
+// Raises the dynamic shared-memory limit of `kernel` the first time it is launched on a device
+// (the attribute belongs to the device's context; setting it on every launch costs microseconds).
+// `done` is the caller's per-kernel flag array, one entry per device: kernels that differ only in
+// template arguments have the same function type, so the flags cannot live in this template.
+constexpr int kMaxDevices = 64;
+using SmemLimitFlags = std::atomic<unsigned char>[kMaxDevices];
+template <typename Kernel>
+inline cudaError_t set_smem_limit_once(Kernel kernel, int bytes, SmemLimitFlags& done) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < kMaxDevices && done[dev].load(std::memory_order_acquire)) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && dev >= 0 && dev < kMaxDevices) done[dev].store(1, std::memory_order_release);
+  return e;
+}
 
 }  // namespace fa

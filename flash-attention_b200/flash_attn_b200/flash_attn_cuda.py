@@ -41,6 +41,33 @@ def _require(cond, msg):
         raise RuntimeError(msg)
 
 
+class _on_device:
+    """`torch.cuda.device(dev)` that costs nothing when `dev` is already current (the usual case;
+    the stock context manager resolves the device twice on every entry)."""
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device):
+        self.idx = device.index
+        self.prev = -1
+
+    def __enter__(self):
+        cur = torch._C._cuda_getDevice()
+        if self.idx is not None and cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
+def _raw_stream():
+    """Handle (cudaStream_t as an integer) of the current stream of the current device."""
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
+
+
 def _philox_state(gen, increment):
     """(seed, offset) of the generator, then advance it by `increment` -- what
     CUDAGeneratorImpl::philox_cuda_state(increment) does in the reference
@@ -55,31 +82,33 @@ def _philox_state(gen, increment):
 
 
 def _check_qkv(q, k, v, cu_seqlens_q, cu_seqlens_k):
+    dt = q.dtype
     _require(q.is_cuda and k.is_cuda and v.is_cuda, "q, k, v must be CUDA tensors")
-    _require(q.dtype in (torch.float16, torch.bfloat16), "q must be fp16 or bf16")
-    _require(k.dtype == q.dtype and v.dtype == q.dtype, "q, k, v must have the same dtype")
-    _require(cu_seqlens_q.dtype == torch.int32 and cu_seqlens_k.dtype == torch.int32,
+    _require(dt is torch.float16 or dt is torch.bfloat16, "q must be fp16 or bf16")
+    _require(k.dtype is dt and v.dtype is dt, "q, k, v must have the same dtype")
+    _require(cu_seqlens_q.dtype is torch.int32 and cu_seqlens_k.dtype is torch.int32,
              "cu_seqlens must be int32")
     _require(cu_seqlens_q.is_cuda and cu_seqlens_k.is_cuda, "cu_seqlens must be CUDA tensors")
     _require(cu_seqlens_q.is_contiguous() and cu_seqlens_k.is_contiguous(),
              "cu_seqlens must be contiguous")
-    _require(q.dim() == 3 and k.dim() == 3 and v.dim() == 3, "q, k, v must be (total, heads, d)")
-    _require(q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1,
+    qs, ks, vs = q.shape, k.shape, v.shape
+    _require(len(qs) == 3 and len(ks) == 3 and len(vs) == 3, "q, k, v must be (total, heads, d)")
+    _require(q.stride(2) == 1 and k.stride(2) == 1 and v.stride(2) == 1,
              "q, k, v must have a contiguous last dimension")
-    batch = cu_seqlens_q.numel() - 1
+    batch = cu_seqlens_q.shape[0] - 1
     _require(batch > 0, "batch size must be positive")
-    _require(cu_seqlens_k.numel() == batch + 1, "cu_seqlens_q / cu_seqlens_k size mismatch")
-    total_q, heads, d = q.shape
-    total_k = k.shape[0]
+    _require(cu_seqlens_k.shape[0] == batch + 1, "cu_seqlens_q / cu_seqlens_k size mismatch")
+    total_q, heads, d = qs
+    total_k = ks[0]
     _require(d in (16, 32, 64, 128), "head_dim must be 16, 32, 64 or 128")
-    _require(tuple(k.shape) == (total_k, heads, d), "k has the wrong shape")
-    _require(tuple(v.shape) == (total_k, heads, d), "v has the wrong shape")
+    _require(ks[1] == heads and ks[2] == d, "k has the wrong shape")
+    _require(vs[0] == total_k and vs[1] == heads and vs[2] == d, "v has the wrong shape")
     return batch, total_q, total_k, heads, d
 
 
-def _fill_fwd(p, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout, scale, causal,
+def _fill_fwd(p, dims, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout, scale, causal,
               seed, offset):
-    batch, total_q, total_k, heads, d = _check_qkv(q, k, v, cu_q, cu_k)
+    batch, total_q, total_k, heads, d = dims
     p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     p.o = o.data_ptr()
     p.softmax_lse = lse.data_ptr()
@@ -133,7 +162,7 @@ def _run_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_
     if sparse:
         _require(not is_causal, "block-sparse attention does not support causal")
         _check_blockmask(blockmask, max_seqlen_q, max_seqlen_k, q)
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         lse_len = _round_up(int(max_seqlen_q), 16)
         if zero_tensors or sparse:  # the block-sparse entry always starts from o = 0 (:519)
             o = torch.zeros((total_q, heads, d), dtype=q.dtype, device=q.device)
@@ -149,8 +178,9 @@ def _run_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_
             inc = lib.fa_philox_increment(d, int(max_seqlen_q), int(max_seqlen_k), int(sparse))
             seed, offset = _philox_state(gen, inc)
         p = FwdParams()
-        _fill_fwd(p, q, k, v, o, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
-                  p_dropout, softmax_scale, is_causal, seed, offset)
+        _fill_fwd(p, (batch, total_q, total_k, heads, d), q, k, v, o, lse, cu_seqlens_q,
+                  cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, is_causal,
+                  seed, offset)
         s_dmask = None
         if return_softmax:
             # (batch, heads, seqlen_q rounded to 16, seqlen_k rounded as the reference does,
@@ -164,7 +194,7 @@ def _run_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_
             p.blockmask = blockmask.data_ptr()
             p.blockmask_rows, p.blockmask_cols = blockmask.shape
             p.bs_workspace, p.bs_workspace_bytes = ws.data_ptr(), ws.numel()
-        check(lib.fa_fwd(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        check(lib.fa_fwd(ctypes.byref(p), _raw_stream()))
     return [o, lse, s_dmask] if return_softmax else [o, lse]
 
 
@@ -231,7 +261,7 @@ def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
              and softmax_lse.shape[2] >= max_seqlen_q and softmax_lse.is_contiguous(),
              "softmax_lse must be a contiguous fp32 (batch, heads, >= max_seqlen_q) tensor")
     _require(p_dropout < 1.0, "p_dropout must be < 1")
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         if zero_tensors:
             dq.zero_()
             dk.zero_()
@@ -244,8 +274,9 @@ def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
             # dummy amount (csrc/flash_attn/fmha_api.cpp:437-445).
             seed, offset = _philox_state(gen, 4)
         p = BwdParams()
-        _fill_fwd(p.fwd, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
-                  max_seqlen_k, p_dropout, softmax_scale, is_causal, seed, offset)
+        _fill_fwd(p.fwd, (batch, total_q, total_k, heads, d), q, k, v, out, softmax_lse,
+                  cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale,
+                  is_causal, seed, offset)
         p.dout = dout.data_ptr()
         p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
         p.softmax_d = softmax_d.data_ptr()
@@ -264,7 +295,7 @@ def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
         p.workspace = ws.data_ptr()
         p.workspace_bytes = ws.numel()
         p.stage_mask = _stage_mask
-        check(lib.fa_bwd(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        check(lib.fa_bwd(ctypes.byref(p), _raw_stream()))
     return [dq, dk, dv, softmax_d]
 
 

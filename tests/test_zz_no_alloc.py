@@ -17,7 +17,8 @@ pytestmark = pytest.mark.gpu
 
 def _bwd_params(fc, _lib, q, k, v, out, lse, dout, grads, softmax_d, cu_q, cu_k, max_q, max_k, scale, causal):
     p = _lib.BwdParams()
-    fc._fill_fwd(p.fwd, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, 0.0, scale, causal, 0, 0)
+    dims = fc._check_qkv(q, k, v, cu_q, cu_k)
+    fc._fill_fwd(p.fwd, dims, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, 0.0, scale, causal, 0, 0)
     p.dout = dout.data_ptr()
     p.dq, p.dk, p.dv = (g.data_ptr() for g in grads)
     p.softmax_d = softmax_d.data_ptr()
