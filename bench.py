@@ -180,6 +180,9 @@ def main():
     ap.add_argument("--seqlen", type=int, default=4096)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--only-extra", default=None, metavar="NAME",
+                    help="run just one entry of the extras sweep (e.g. causal_lm_bf16_d128_S4096) and "
+                         "print it; for profiler captures of the other configurations")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the host-buffer and CPU legs (for profiler runs)")
     args = ap.parse_args()
@@ -202,6 +205,10 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.only_extra:
+        print(json.dumps({"extras": extras(fc, dev, measured_peaks(), only=args.only_extra)}), flush=True)
+        return
 
     # ------------------------------------------------------------------ synthetic workload
     lengths = workload_lengths(args.seqlen, args.seed)          # same lengths on every rank
@@ -410,10 +417,14 @@ def main():
         dist.destroy_process_group()
 
 
-def extras(fc, dev, peaks):
+def extras(fc, dev, peaks, only=None):
     """Short sweeps over the other benchmark configurations (few iterations each, kernel time
-    only, data resident): reported for context, not part of the headline value."""
+    only, data resident): reported for context, not part of the headline value.  `only` limits
+    the sweep to one named entry."""
     res = {}
+
+    def wanted(name):
+        return only is None or only == name
 
     def time_fwd_bwd(q, k, v, dout, cu, S, p, causal, scale, iters=5):
         out, lse = fc.fwd(q, k, v, cu, cu, S, S, p, scale, False, causal, False, None)
@@ -436,6 +447,8 @@ def extras(fc, dev, peaks):
     g = torch.Generator(device=dev).manual_seed(5)
     # BERT-base varlen sweep (fp16, dropout 0.1)
     for S in (128, 256, 512, 1024, 2048, 4096):
+        if not wanted("bert_varlen_fp16_dropout_S%d" % S):
+            continue
         lengths = workload_lengths(S, 0)
         total = sum(lengths)
         cu = torch.tensor(np.concatenate([[0], np.cumsum(lengths)]), dtype=torch.int32, device=dev)
@@ -455,6 +468,8 @@ def extras(fc, dev, peaks):
         res["bert_varlen_fp16_dropout_S%d" % S] = entry
     # causal LM (bf16, d = 128)
     for S in (512, 1024, 2048, 4096, 8192):
+        if not wanted("causal_lm_bf16_d128_S%d" % S):
+            continue
         B, H, d = 16, 12, 128
         cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=dev)
         q = torch.randn(B * S, H, d, device=dev, dtype=torch.bfloat16, generator=g)
@@ -464,6 +479,59 @@ def extras(fc, dev, peaks):
         f, b = time_fwd_bwd(q, k, v, dout, cu, S, 0.0, True, d ** -0.5, iters=3)
         fl = fwd_flops([S] * B, H, d, causal=True)
         res["causal_lm_bf16_d128_S%d" % S] = {
+            "fwd_ms": f, "bwd_ms": b, "fwd_tflops": fl / f / 1e9, "fwd_bwd_tflops": 3.5 * fl / (f + b) / 1e9,
+            "fwd_pct_peak": 100 * fl / f / 1e9 / peaks["tflops"],
+            "fwd_bwd_pct_peak": 100 * 3.5 * fl / (f + b) / 1e9 / peaks["tflops"]}
+        del q, k, v, dout
+    # block-sparse (fp16, d = 64, 256 x 256 blocks at 25 % density + diagonal, dropout 0.1)
+    if wanted("blocksparse_fp16_d64_S4096"):
+        from flash_attn_b200.flash_blocksparse_attn_interface import convert_blockmask
+        B, H, d, S = 4, 16, 64, 4096
+        nb = S // 256
+        gl = torch.Generator().manual_seed(7)
+        blocks = (torch.rand(nb, nb, generator=gl) < 0.25) | torch.eye(nb, dtype=torch.bool)
+        layout = blocks.repeat_interleave(16, dim=0).to(torch.int32).to(dev)   # (16-row blocks, key blocks)
+        conv = convert_blockmask(layout, False)
+        cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=dev)
+        q = torch.randn(B * S, H, d, device=dev, dtype=torch.float16, generator=g)
+        k = torch.randn(B * S, H, d, device=dev, dtype=torch.float16, generator=g)
+        v = torch.randn(B * S, H, d, device=dev, dtype=torch.float16, generator=g)
+        dout = torch.randn(B * S, H, d, device=dev, dtype=torch.float16, generator=g)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        out, lse = fc.fwd_block(q, k, v, cu, cu, conv, S, S, DROPOUT_P, 0.125, False, False, None)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        for it in range(2):
+            if it == 1:
+                torch.cuda.synchronize()
+                ev[0].record()
+            for _ in range(3):
+                fc.fwd_block(q, k, v, cu, cu, conv, S, S, DROPOUT_P, 0.125, False, False, None)
+            if it == 1:
+                ev[1].record()
+            for _ in range(3):
+                fc.bwd_block(dout, q, k, v, out, lse, dq, dk, dv, cu, cu, conv, S, S, DROPOUT_P, 0.125,
+                             False, None)
+        ev[2].record()
+        torch.cuda.synchronize()
+        f, b = ev[0].elapsed_time(ev[1]) / 3, ev[1].elapsed_time(ev[2]) / 3
+        density = float(blocks.float().mean())
+        fl = 4.0 * d * H * B * float(S) * float(S) * density   # work of the blocks in the layout
+        res["blocksparse_fp16_d64_S4096"] = {
+            "fwd_ms": f, "bwd_ms": b, "layout_density": density, "fwd_tflops": fl / f / 1e9,
+            "fwd_bwd_tflops": 3.5 * fl / (f + b) / 1e9,
+            "fwd_bwd_pct_peak": 100 * 3.5 * fl / (f + b) / 1e9 / peaks["tflops"]}
+        del q, k, v, dout, dq, dk, dv
+    # long context, one GPU's share of an 8-way head shard (batch 2, 32 / 8 = 4 heads, d = 64, causal, bf16)
+    if wanted("long_context_bf16_d64_S65536_4heads"):
+        B, H, d, S = 2, 4, 64, 65536
+        cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=dev)
+        q = torch.randn(B * S, H, d, device=dev, dtype=torch.bfloat16, generator=g)
+        k = torch.randn(B * S, H, d, device=dev, dtype=torch.bfloat16, generator=g)
+        v = torch.randn(B * S, H, d, device=dev, dtype=torch.bfloat16, generator=g)
+        dout = torch.randn(B * S, H, d, device=dev, dtype=torch.bfloat16, generator=g)
+        f, b = time_fwd_bwd(q, k, v, dout, cu, S, 0.0, True, 0.125, iters=2)
+        fl = fwd_flops([S] * B, H, d, causal=True)
+        res["long_context_bf16_d64_S65536_4heads"] = {
             "fwd_ms": f, "bwd_ms": b, "fwd_tflops": fl / f / 1e9, "fwd_bwd_tflops": 3.5 * fl / (f + b) / 1e9,
             "fwd_pct_peak": 100 * fl / f / 1e9 / peaks["tflops"],
             "fwd_bwd_pct_peak": 100 * 3.5 * fl / (f + b) / 1e9 / peaks["tflops"]}

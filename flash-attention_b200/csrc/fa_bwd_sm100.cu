@@ -85,12 +85,6 @@ struct BwdShared {
   int abort_flag;
 };
 
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
   if constexpr (BF16) {
@@ -100,12 +94,6 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
   }
-}
-
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
-               "f"(d)
-               : "memory");
 }
 
 // Optional cycle accounting (build with -DFA_PROFILE): one thread of each role of CTA (0,0,0)

@@ -113,54 +113,6 @@ __host__ __device__ __forceinline__ uint32_t fa_dropout_keep16(const DropoutPara
 
 namespace fa {
 
-// Round keys of the seven Philox rounds: the same for every call of a launch, so a thread keeps
-// them in registers.
-struct PhiloxKeys {
-  uint32_t k0[7], k1[7];
-  __host__ __device__ __forceinline__ void init(uint32_t key0, uint32_t key1) {
-#pragma unroll
-    for (int r = 0; r < 7; ++r) {
-      k0[r] = key0 + static_cast<uint32_t>(r) * 0x9E3779B9u;
-      k1[r] = key1 + static_cast<uint32_t>(r) * 0xBB67AE85u;
-    }
-  }
-};
-
-// One Philox call for (row i, 16-column group starting at jg0, quarter q): all four output words.
-// Words 0,1 belong to the row with (i % 16) < 8, words 2,3 to the row 8 below it; within a pair the
-// first word covers columns {2q, 2q+1}, the second {2q+8, 2q+9} (low half = even column).
-__host__ __device__ __forceinline__ void fa_philox_call(const DropoutParams& dp, const PhiloxKeys& pk,
-                                                        int64_t bh_sub, int32_t i, int32_t jg0, int32_t q,
-                                                        int64_t iter_index, uint32_t (&c)[4]) {
-  const int32_t n_mask = (1 << dp.n_shift) - 1;
-  const int32_t c16 = (jg0 & n_mask) >> 4;
-  const uint64_t subseq = static_cast<uint64_t>(bh_sub) + (c16 & 7) * 32 + (i & 7) * 4 + q;
-  const uint64_t ctr = dp.counter_base + static_cast<uint64_t>(iter_index << (dp.n_shift - 7)) +
-                       static_cast<uint64_t>(c16 >> 3);
-  c[0] = static_cast<uint32_t>(ctr);
-  c[1] = static_cast<uint32_t>(ctr >> 32);
-  c[2] = static_cast<uint32_t>(subseq);
-  c[3] = static_cast<uint32_t>(subseq >> 32);
-#pragma unroll
-  for (int r = 0; r < 7; ++r) philox_round(c, pk.k0[r], pk.k1[r]);
-}
-
-// Counter words of that call without running the rounds (for callers that interleave the rounds
-// of many independent calls).
-__host__ __device__ __forceinline__ void fa_philox_init(const DropoutParams& dp, int64_t bh_sub, int32_t i,
-                                                        int32_t jg0, int32_t q, int64_t iter_index,
-                                                        uint32_t (&c)[4]) {
-  const int32_t n_mask = (1 << dp.n_shift) - 1;
-  const int32_t c16 = (jg0 & n_mask) >> 4;
-  const uint64_t subseq = static_cast<uint64_t>(bh_sub) + (c16 & 7) * 32 + (i & 7) * 4 + q;
-  const uint64_t ctr = dp.counter_base + static_cast<uint64_t>(iter_index << (dp.n_shift - 7)) +
-                       static_cast<uint64_t>(c16 >> 3);
-  c[0] = static_cast<uint32_t>(ctr);
-  c[1] = static_cast<uint32_t>(ctr >> 32);
-  c[2] = static_cast<uint32_t>(subseq);
-  c[3] = static_cast<uint32_t>(subseq >> 32);
-}
-
 #ifdef __CUDACC__
 // ---------------------------------------------------------------------------------------------
 // Row-per-thread mask generation (the layout of the attention kernels: lane = query row).

@@ -52,12 +52,6 @@ struct FwdShared {
   int abort_flag;
 };
 
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 // Optional cycle accounting (build with -DFA_PROFILE): thread 0 of softmax group 0 and the MMA
 // thread of CTA (0,0,0) accumulate the cycles they spend in each phase into status[8..].
 #ifdef FA_PROFILE

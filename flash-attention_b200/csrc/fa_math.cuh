@@ -54,12 +54,4 @@ __device__ __forceinline__ uint32_t pack_lowp(float lo, float hi) {
   return r;
 }
 
-// 32-bit mask for a packed pair of 16-bit values: low half kept iff (w & 0xffff) <= thr,
-// high half kept iff (w >> 16) <= thr.  `thr_hi_excl` = (thr + 1) << 16.
-__device__ __forceinline__ uint32_t keep_mask_pair(uint32_t w, uint32_t thr, uint32_t thr_hi_excl) {
-  const uint32_t lo = ((w & 0xffffu) <= thr) ? 0x0000ffffu : 0u;
-  const uint32_t hi = (w < thr_hi_excl) ? 0xffff0000u : 0u;
-  return lo | hi;
-}
-
 }  // namespace fa
