@@ -444,6 +444,47 @@ def extras(fc, dev, peaks, only=None):
         torch.cuda.synchronize()
         return ev[0].elapsed_time(ev[1]) / iters, ev[1].elapsed_time(ev[2]) / iters
 
+    def graph_times(q, k, v, dout, cu, S, p, causal, scale, reps=10):
+        """GPU time per call without the host in the loop: `reps` forward (then backward) calls of
+        the C ABI captured in a CUDA graph and replayed.  Short sequences are otherwise timed at
+        the speed of the Python binding (tens of microseconds per call)."""
+        import ctypes
+        from flash_attn_b200 import _lib
+        out, lse = fc.fwd(q, k, v, cu, cu, S, S, p, scale, False, causal, False, None)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        softmax_d = torch.empty_like(lse)
+        dims = fc._check_qkv(q, k, v, cu, cu)
+        pf = _lib.FwdParams()
+        fc._fill_fwd(pf, dims, q, k, v, out, lse, cu, cu, S, S, p, scale, causal, 1234, 0)
+        pb = _lib.BwdParams()
+        fc._fill_fwd(pb.fwd, dims, q, k, v, out, lse, cu, cu, S, S, p, scale, causal, 1234, 0)
+        pb.dout, pb.softmax_d = dout.data_ptr(), softmax_d.data_ptr()
+        pb.dq, pb.dk, pb.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+        pb.dq_row_stride, pb.dq_head_stride = dq.stride(0), dq.stride(1)
+        pb.dk_row_stride, pb.dk_head_stride = dk.stride(0), dk.stride(1)
+        pb.dv_row_stride, pb.dv_head_stride = dv.stride(0), dv.stride(1)
+        ws = torch.empty(_lib.lib.fa_bwd_workspace_bytes(dims[1], dims[3], dims[4]), dtype=torch.uint8, device=q.device)
+        pb.workspace, pb.workspace_bytes = ws.data_ptr(), ws.numel()
+        times = []
+        side_stream = torch.cuda.Stream(device=q.device)
+        for call, params in ((_lib.lib.fa_fwd, pf), (_lib.lib.fa_bwd, pb)):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side_stream):
+                _lib.check(call(ctypes.byref(params), fc._raw_stream()))   # first use outside capture
+                torch.cuda.synchronize()
+                with torch.cuda.graph(graph, stream=side_stream):
+                    for _ in range(reps):
+                        _lib.check(call(ctypes.byref(params), fc._raw_stream()))
+            graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) / reps)
+        return times[0], times[1]
+
     g = torch.Generator(device=dev).manual_seed(5)
     # BERT-base varlen sweep (fp16, dropout 0.1)
     for S in (128, 256, 512, 1024, 2048, 4096):
@@ -459,12 +500,16 @@ def extras(fc, dev, peaks, only=None):
         entry = {"fwd_ms": f, "bwd_ms": b, "fwd_tflops": fl / f / 1e9, "fwd_bwd_tflops": 3.5 * fl / (f + b) / 1e9,
                  "fwd_bwd_pct_peak": 100 * 3.5 * fl / (f + b) / 1e9 / peaks["tflops"]}
         if S <= 512:
+            # short sequences: also the GPU time alone (graph replay), and HBM GB/s from it
+            fg, bg = graph_times(qkv[:, 0], qkv[:, 1], qkv[:, 2], dout, cu, S, DROPOUT_P, False, 0.125)
             hd = HEADS * HEAD_DIM
             fwd_bytes = 2 * 3 * total * hd + 2 * total * hd + 4 * BATCH * HEADS * S
             bwd_bytes = 2 * hd * 5 * total + 2 * hd * 3 * total + 8 * BATCH * HEADS * S
-            entry["fwd_gbs"] = fwd_bytes / f / 1e6
-            entry["bwd_gbs"] = bwd_bytes / b / 1e6
-            entry["fwd_pct_hbm_peak"] = 100 * fwd_bytes / f / 1e6 / peaks["hbm_gbs"]
+            entry["fwd_gpu_ms"], entry["bwd_gpu_ms"] = fg, bg
+            entry["fwd_bwd_gpu_tflops"] = 3.5 * fl / (fg + bg) / 1e9
+            entry["fwd_gbs"] = fwd_bytes / fg / 1e6
+            entry["bwd_gbs"] = bwd_bytes / bg / 1e6
+            entry["fwd_pct_hbm_peak"] = 100 * fwd_bytes / fg / 1e6 / peaks["hbm_gbs"]
         res["bert_varlen_fp16_dropout_S%d" % S] = entry
     # causal LM (bf16, d = 128)
     for S in (512, 1024, 2048, 4096, 8192):
