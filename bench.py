@@ -566,6 +566,48 @@ def extras(fc, dev, peaks, only=None):
             "fwd_bwd_tflops": 3.5 * fl / (f + b) / 1e9,
             "fwd_bwd_pct_peak": 100 * 3.5 * fl / (f + b) / 1e9 / peaks["tflops"]}
         del q, k, v, dout, dq, dk, dv
+    # padding helpers (HBM bound): unpad = row gather, pad = row scatter over zeros
+    if wanted("unpad_pad_fp16_B64_S512_D2304"):
+        from flash_attn_b200 import bert_padding as bp
+        B, S, D = 64, 512, 2304
+        lengths = torch.tensor(workload_lengths(S, 0, batch=B), device=dev)
+        mask = torch.arange(S, device=dev)[None, :] < lengths[:, None]
+        idx = torch.nonzero(mask.flatten(), as_tuple=False).flatten()
+        x = torch.randn(B * S, D, device=dev, dtype=torch.float16, generator=g)
+        packed = bp.gather_rows(x, idx)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        for it in range(2):
+            if it == 1:
+                torch.cuda.synchronize()
+                ev[0].record()
+            for _ in range(5):
+                bp.gather_rows(x, idx)
+            if it == 1:
+                ev[1].record()
+            for _ in range(5):
+                bp.scatter_rows(packed, idx, B * S)
+            if it == 1:
+                ev[2].record()
+            for _ in range(5):
+                x.index_select(0, idx)
+            if it == 1:
+                ev[3].record()
+            for _ in range(5):
+                x.new_zeros((B * S, D)).index_copy_(0, idx, packed)
+        ev[4].record()
+        torch.cuda.synchronize()
+        row = D * 2
+        n = idx.numel()
+        t = [ev[i].elapsed_time(ev[i + 1]) / 5 for i in range(4)]
+        gather_bytes = 2 * n * row + 8 * n                 # rows read + written, indices
+        scatter_bytes = n * row + B * S * row + 8 * n + 8 * B * S   # rows read, output written once, index maps
+        res["unpad_pad_fp16_B64_S512_D2304"] = {
+            "tokens": n, "gather_ms": t[0], "scatter_ms": t[1],
+            "gather_gbs": gather_bytes / t[0] / 1e6, "scatter_gbs": scatter_bytes / t[1] / 1e6,
+            "gather_frac_hbm_peak": gather_bytes / t[0] / 1e6 / peaks["hbm_gbs"],
+            "scatter_frac_hbm_peak": scatter_bytes / t[1] / 1e6 / peaks["hbm_gbs"],
+            "torch_index_select_ms": t[2], "torch_zeros_index_copy_ms": t[3]}
+        del x, packed
     # long context, one GPU's share of an 8-way head shard (batch 2, 32 / 8 = 4 heads, d = 64, causal, bf16)
     if wanted("long_context_bf16_d64_S65536_4heads"):
         B, H, d, S = 2, 4, 64, 65536

@@ -17,7 +17,7 @@ OUT_DIR = os.path.join(HERE, "flash_attn_b200")
 LIB_PATH = os.path.join(OUT_DIR, "libfa_b200.so")
 OBJ_DIR = os.path.join(HERE, "build")
 
-SOURCES = ["fa_api.cu", "fa_fwd_sm100.cu", "fa_bwd_sm100.cu", "fa_aux.cu"]
+SOURCES = ["fa_api.cu", "fa_fwd_sm100.cu", "fa_bwd_sm100.cu", "fa_aux.cu", "fa_padding.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

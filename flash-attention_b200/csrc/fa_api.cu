@@ -181,6 +181,34 @@ void fill_args(const fa_fwd_params* p, fa::KernelArgs* a) {
 
 extern "C" {
 
+int fa_gather_rows(const void* src, const int64_t* indices, void* dst, int64_t n_rows,
+                   int64_t src_rows, int64_t row_bytes, void* cuda_stream) {
+  FA_REQUIRE(n_rows >= 0 && src_rows >= 0 && row_bytes >= 0, "negative size");
+  if (n_rows == 0 || row_bytes == 0) return FA_OK;
+  FA_REQUIRE(src && indices && dst, "src, indices and dst must be non-null");
+  FA_REQUIRE(row_bytes % 16 == 0, "row_bytes must be a multiple of 16");
+  FA_REQUIRE(((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0,
+             "src and dst must be 16-byte aligned");
+  FA_CUDA(fa::launch_gather_rows(src, indices, dst, n_rows, src_rows, row_bytes,
+                                 static_cast<cudaStream_t>(cuda_stream)));
+  return FA_OK;
+}
+
+int fa_scatter_rows(const void* src, const int64_t* indices, void* dst, int64_t n_src_rows,
+                    int64_t n_dst_rows, int64_t row_bytes, int32_t* workspace, void* cuda_stream) {
+  FA_REQUIRE(n_src_rows >= 0 && n_dst_rows >= 0 && row_bytes >= 0, "negative size");
+  if (n_dst_rows == 0 || row_bytes == 0) return FA_OK;
+  FA_REQUIRE(dst && workspace, "dst and workspace must be non-null");
+  FA_REQUIRE(n_src_rows == 0 || (src && indices), "src and indices must be non-null");
+  FA_REQUIRE(n_src_rows <= 0x7fffffffLL, "too many source rows");
+  FA_REQUIRE(row_bytes % 16 == 0, "row_bytes must be a multiple of 16");
+  FA_REQUIRE(((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0,
+             "src and dst must be 16-byte aligned");
+  FA_CUDA(fa::launch_scatter_rows(src, indices, dst, n_src_rows, n_dst_rows, row_bytes, workspace,
+                                  static_cast<cudaStream_t>(cuda_stream)));
+  return FA_OK;
+}
+
 const char* fa_status_string(int status) {
   switch (status) {
     case FA_OK: return "ok";

@@ -74,6 +74,12 @@ cudaError_t launch_dropout_mask(uint8_t* out, int b, int h, const DropoutParams&
                                 int sq, int sk, const int32_t* bs_iter, int bs_kblocks,
                                 int bs_rows16, cudaStream_t stream);
 
+cudaError_t launch_gather_rows(const void* src, const int64_t* indices, void* dst, int64_t n_rows,
+                               int64_t src_rows, int64_t row_bytes, cudaStream_t stream);
+cudaError_t launch_scatter_rows(const void* src, const int64_t* indices, void* dst, int64_t n_src_rows,
+                                int64_t n_dst_rows, int64_t row_bytes, int32_t* inverse,
+                                cudaStream_t stream);
+
 // Raises the dynamic shared-memory limit of `kernel` the first time it is launched on a device
 // (the attribute belongs to the device's context; setting it on every launch costs microseconds).
 // `done` is the caller's per-kernel flag array, one entry per device: kernels that differ only in

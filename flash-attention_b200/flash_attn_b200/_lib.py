@@ -26,6 +26,8 @@ EXPORTED_SYMBOLS = (
     "fa_mask_block_n",
     "fa_debug_dropout_mask",
     "fa_debug_philox",
+    "fa_gather_rows",
+    "fa_scatter_rows",
     "fa_status_string",
     "fa_last_error",
     "fa_device_supported",
@@ -126,6 +128,12 @@ def _load():
     lib.fa_debug_philox.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_uint64, ctypes.c_uint64,
                                     ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
     lib.fa_debug_philox.restype = ctypes.c_int
+    lib.fa_gather_rows.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                   ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]
+    lib.fa_gather_rows.restype = ctypes.c_int
+    lib.fa_scatter_rows.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                    ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
+    lib.fa_scatter_rows.restype = ctypes.c_int
     lib.fa_status_string.argtypes = [ctypes.c_int]
     lib.fa_status_string.restype = ctypes.c_char_p
     lib.fa_last_error.argtypes = []

@@ -2,10 +2,56 @@
 
 `unpad_input` turns a padded (batch, seqlen, dim) tensor plus a validity mask into the packed
 (total, dim) layout with int32 cu_seqlens that the attention functions take; `pad_input` is its
-inverse.  Both are differentiable.
+inverse.  Both are differentiable.  On CUDA tensors the row gather / scatter behind them runs as
+one HBM-bound pass of the library's own kernels (fa_gather_rows / fa_scatter_rows).
 """
+import ctypes
+
 import torch
 import torch.nn.functional as F
+
+from ._lib import check, lib
+
+
+def _kernel_path(values, indices):
+    """The row kernels of the library take CUDA tensors with contiguous rows of a multiple of 16
+    bytes and int64 indices; anything else (CPU tensors in particular) goes through framework
+    indexing, which is what the reference always does."""
+    return (values.is_cuda and indices.is_cuda and indices.dtype is torch.int64
+            and values.dim() == 2 and values.is_contiguous() and indices.is_contiguous()
+            and (values.shape[1] * values.element_size()) % 16 == 0 and values.data_ptr() % 16 == 0)
+
+
+def _stream(device):
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(device.index))
+
+
+def gather_rows(values, indices):
+    """values[indices] for a 2-D `values`: one pass, 16-byte accesses."""
+    if not _kernel_path(values, indices):
+        return values.index_select(0, indices)
+    out = torch.empty((indices.shape[0], values.shape[1]), dtype=values.dtype, device=values.device)
+    with torch.cuda.device(values.device):
+        check(lib.fa_gather_rows(values.data_ptr(), indices.data_ptr(), out.data_ptr(), indices.shape[0],
+                                 values.shape[0], values.shape[1] * values.element_size(),
+                                 _stream(values.device)))
+    return out
+
+
+def scatter_rows(values, indices, first_axis_dim):
+    """(first_axis_dim, dim) tensor of zeros with rows `indices` set to `values`: the zero fill and
+    the copy are one pass over the output."""
+    if not _kernel_path(values, indices):
+        out = values.new_zeros((first_axis_dim, values.shape[1]))
+        out.index_copy_(0, indices, values)
+        return out
+    out = torch.empty((first_axis_dim, values.shape[1]), dtype=values.dtype, device=values.device)
+    inverse = torch.empty(max(first_axis_dim, 1), dtype=torch.int32, device=values.device)
+    with torch.cuda.device(values.device):
+        check(lib.fa_scatter_rows(values.data_ptr(), indices.data_ptr(), out.data_ptr(), values.shape[0],
+                                  first_axis_dim, values.shape[1] * values.element_size(),
+                                  inverse.data_ptr(), _stream(values.device)))
+    return out
 
 
 class IndexFirstAxis(torch.autograd.Function):
@@ -16,14 +62,12 @@ class IndexFirstAxis(torch.autograd.Function):
         assert input.ndim == 2
         ctx.save_for_backward(indices)
         ctx.first_axis_dim = input.shape[0]
-        return input.index_select(0, indices)
+        return gather_rows(input, indices)
 
     @staticmethod
     def backward(ctx, grad_output):
         (indices,) = ctx.saved_tensors
-        grad_input = grad_output.new_zeros((ctx.first_axis_dim,) + tuple(grad_output.shape[1:]))
-        grad_input.index_copy_(0, indices, grad_output)
-        return grad_input, None
+        return scatter_rows(grad_output.contiguous(), indices, ctx.first_axis_dim), None
 
 
 index_first_axis = IndexFirstAxis.apply
@@ -36,14 +80,12 @@ class IndexPutFirstAxis(torch.autograd.Function):
     def forward(ctx, values, indices, first_axis_dim):
         assert indices.ndim == 1 and values.ndim == 2
         ctx.save_for_backward(indices)
-        output = values.new_zeros((first_axis_dim, values.shape[1]))
-        output.index_copy_(0, indices, values)
-        return output
+        return scatter_rows(values, indices, first_axis_dim)
 
     @staticmethod
     def backward(ctx, grad_output):
         (indices,) = ctx.saved_tensors
-        return grad_output.index_select(0, indices), None, None
+        return gather_rows(grad_output.contiguous(), indices), None, None
 
 
 index_put_first_axis = IndexPutFirstAxis.apply

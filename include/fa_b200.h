@@ -168,6 +168,22 @@ int fa_debug_dropout_mask(uint8_t* mask_out, int32_t batch_idx, int32_t head_idx
 int fa_debug_philox(uint32_t* out, int32_t n, uint64_t seed, uint64_t offset, int32_t rounds,
                     int32_t use_curand, void* cuda_stream);
 
+/* Row gather for the padding helpers: dst[r, :] = src[indices[r], :] for r < n_rows, rows of
+ * `row_bytes` bytes (a multiple of 16; src and dst 16-byte aligned, rows contiguous).  Replaces the
+ * framework indexing in flash_attn/bert_padding.py:14-19 (IndexFirstAxis.forward, used by
+ * unpad_input :60-80) and :50-54 (IndexPutFirstAxis.backward).  An index outside [0, src_rows)
+ * yields a zero row. */
+int fa_gather_rows(const void* src, const int64_t* indices, void* dst, int64_t n_rows,
+                   int64_t src_rows, int64_t row_bytes, void* cuda_stream);
+
+/* Row scatter over zeros: dst (n_dst_rows rows) = 0 except dst[indices[r], :] = src[r, :] for
+ * r < n_src_rows, written in one pass.  Replaces flash_attn/bert_padding.py:40-45
+ * (IndexPutFirstAxis.forward, used by pad_input :83-95) and :22-29 (IndexFirstAxis.backward).
+ * `workspace` holds n_dst_rows int32 (the inverse index map).  Indices outside [0, n_dst_rows) are
+ * skipped; with duplicate indices one of the source rows wins. */
+int fa_scatter_rows(const void* src, const int64_t* indices, void* dst, int64_t n_src_rows,
+                    int64_t n_dst_rows, int64_t row_bytes, int32_t* workspace, void* cuda_stream);
+
 const char* fa_status_string(int status);
 const char* fa_last_error(void);
 
