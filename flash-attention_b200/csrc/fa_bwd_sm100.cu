@@ -147,7 +147,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const int n0 = nt * kBN;
   if (n0 >= sk) return;
   // fail fast: once a CTA of this launch has abandoned a wait, the remaining CTAs do not start
-  if (ka.status && *reinterpret_cast<volatile int32_t*>(ka.status) != 0) return;
+  if (ka.status && *reinterpret_cast<volatile int32_t*>(ka.status) == ka.launch_id) return;
 
   const int m_tiles = (sq + kBM - 1) / kBM;
   const int m_begin = CAUSAL ? min(m_tiles, n0 / kBM) : 0;
@@ -887,7 +887,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   if (warp == 12) {
     tmem_dealloc(tmem, 512);
     if (lane == 0 && sh.abort_flag && ka.status) {
-      atomicExch(ka.status, 1);      // launch-local: stops CTAs that have not started yet
+      atomicExch(ka.status, ka.launch_id);  // stops the CTAs of this launch that have not started yet
       atomicExch(ka.status + 3, 1);  // sticky: read by the host
     }
   }

@@ -109,7 +109,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const int sk = a.cu_seqlens_k[b + 1] - k_start;
   if (mp * 2 * kBlockM >= sq) return;
   // fail fast: once a CTA of this launch has abandoned a wait, the remaining CTAs do not start
-  if (a.status && *reinterpret_cast<volatile int32_t*>(a.status) != 0) return;
+  if (a.status && *reinterpret_cast<volatile int32_t*>(a.status) == a.launch_id) return;
 
   int n_kv_total = (sk + kBlockN - 1) / kBlockN;
   if constexpr (BLOCKSPARSE) {
@@ -567,7 +567,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   if (warp == 8) {
     tmem_dealloc(tmem, 512);
     if (lane == 0 && sh.abort_flag && a.status) {
-      atomicExch(a.status, 1);      // launch-local: stops CTAs that have not started yet
+      atomicExch(a.status, a.launch_id);  // stops the CTAs of this launch that have not started yet
       atomicExch(a.status + 2, 1);  // sticky: read by the host
     }
   }

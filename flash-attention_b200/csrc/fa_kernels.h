@@ -27,6 +27,7 @@ struct KernelArgs {
   float rp_keep;      // 1 / p_keep
   DropoutParams drop;
   int32_t* status;
+  int32_t launch_id;  // non-zero serial number of this call: what an aborting CTA leaves in status[0]
 };
 
 struct BwdArgs {

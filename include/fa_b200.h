@@ -74,9 +74,10 @@ typedef struct fa_fwd_params {
   /* Head count / first head used in the Philox subsequence, for callers that shard heads across
    * devices and want the mask of the unsharded call.  0 / 0 means (heads, 0). */
   int32_t mask_heads_total, mask_head_offset;
-  /* Optional device int32[4].  Word 0 is cleared by every launch and set by a CTA that abandons a
-   * bounded wait, which also keeps the CTAs of that launch that have not started from starting;
-   * words 2 (forward) and 3 (backward) are set at the same time and never cleared by the library. */
+  /* Optional device int32[4].  A CTA that abandons a bounded wait writes the (non-zero) serial
+   * number of its launch into word 0, which keeps the CTAs of that launch that have not started
+   * from starting; words 2 (forward) and 3 (backward) are set to 1 at the same time and never
+   * cleared by the library. */
   int32_t* status;
   /* Block-sparse only: device scratch of fa_blocksparse_workspace_bytes() for the per-sequence
    * block-visit table the call derives from blockmask and cu_seqlens. */
