@@ -132,6 +132,20 @@ def _fill_fwd(p, dims, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout, sca
     p.status = _status_buffer(q.device).data_ptr()
 
 
+def _make_fwd(dims, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout, scale, causal, seed, offset):
+    """FwdParams filled through the structure's positional constructor (one call instead of forty
+    attribute stores): the per-call host time of short-sequence workloads is mostly this binding."""
+    batch, total_q, total_k, heads, d = dims
+    qs, ks, vs, os_ = q.stride(), k.stride(), v.stride(), o.stride()
+    return FwdParams(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                     cu_q.data_ptr(), cu_k.data_ptr(), None, None, 0, 0,
+                     qs[0], qs[1], ks[0], ks[1], vs[0], vs[1], os_[0], os_[1], lse.shape[-1],
+                     batch, heads, d, total_q, total_k, int(max_q), int(max_k),
+                     float(p_dropout), float(scale), 1 if causal else 0,
+                     1 if q.dtype is torch.bfloat16 else 0, seed, offset, 0, 0,
+                     _status_buffer(q.device).data_ptr(), None, 0, 0, 0)
+
+
 def _round_up(x, m):
     return (x + m - 1) // m * m
 
@@ -177,10 +191,9 @@ def _run_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_
         if p_dropout > 0:
             inc = lib.fa_philox_increment(d, int(max_seqlen_q), int(max_seqlen_k), int(sparse))
             seed, offset = _philox_state(gen, inc)
-        p = FwdParams()
-        _fill_fwd(p, (batch, total_q, total_k, heads, d), q, k, v, o, lse, cu_seqlens_q,
-                  cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, is_causal,
-                  seed, offset)
+        p = _make_fwd((batch, total_q, total_k, heads, d), q, k, v, o, lse, cu_seqlens_q,
+                      cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, is_causal,
+                      seed, offset)
         s_dmask = None
         if return_softmax:
             # (batch, heads, seqlen_q rounded to 16, seqlen_k rounded as the reference does,
@@ -245,20 +258,18 @@ def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
     """mha_bwd (csrc/flash_attn/fmha_api.cpp:302-449): writes dq, dk, dv in place and returns
     [dq, dk, dv, softmax_d]."""
     batch, total_q, total_k, heads, d = _check_qkv(q, k, v, cu_seqlens_q, cu_seqlens_k)
-    _require(dout.dtype == q.dtype and out.dtype == q.dtype, "dout / out dtype mismatch")
-    _require(dq.dtype == q.dtype and dk.dtype == q.dtype and dv.dtype == q.dtype,
-             "dq / dk / dv dtype mismatch")
+    dt, qshape, kshape = q.dtype, q.shape, k.shape
+    _require(dout.dtype is dt and out.dtype is dt, "dout / out dtype mismatch")
+    _require(dq.dtype is dt and dk.dtype is dt and dv.dtype is dt, "dq / dk / dv dtype mismatch")
     _require(out.is_contiguous() and dout.is_contiguous(), "out and dout must be contiguous")
-    _require(tuple(out.shape) == (total_q, heads, d) and tuple(dout.shape) == (total_q, heads, d),
-             "out / dout have the wrong shape")
-    _require(tuple(dq.shape) == (total_q, heads, d), "dq has the wrong shape")
-    _require(tuple(dk.shape) == (total_k, heads, d) and tuple(dv.shape) == (total_k, heads, d),
-             "dk / dv have the wrong shape")
-    _require(dq.stride(-1) == 1 and dk.stride(-1) == 1 and dv.stride(-1) == 1,
+    _require(out.shape == qshape and dout.shape == qshape, "out / dout have the wrong shape")
+    _require(dq.shape == qshape, "dq has the wrong shape")
+    _require(dk.shape == kshape and dv.shape == kshape, "dk / dv have the wrong shape")
+    _require(dq.stride(2) == 1 and dk.stride(2) == 1 and dv.stride(2) == 1,
              "dq, dk, dv must have a contiguous last dimension")
-    _require(softmax_lse.dtype == torch.float32 and softmax_lse.dim() == 3
-             and softmax_lse.shape[0] == batch and softmax_lse.shape[1] == heads
-             and softmax_lse.shape[2] >= max_seqlen_q and softmax_lse.is_contiguous(),
+    lshape = softmax_lse.shape
+    _require(softmax_lse.dtype is torch.float32 and len(lshape) == 3 and lshape[0] == batch
+             and lshape[1] == heads and lshape[2] >= max_seqlen_q and softmax_lse.is_contiguous(),
              "softmax_lse must be a contiguous fp32 (batch, heads, >= max_seqlen_q) tensor")
     _require(p_dropout < 1.0, "p_dropout must be < 1")
     with _on_device(q.device):
@@ -273,16 +284,15 @@ def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
             # state here yields the forward's (seed, offset); the reference then advances it by a
             # dummy amount (csrc/flash_attn/fmha_api.cpp:437-445).
             seed, offset = _philox_state(gen, 4)
-        p = BwdParams()
-        _fill_fwd(p.fwd, (batch, total_q, total_k, heads, d), q, k, v, out, softmax_lse,
-                  cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale,
-                  is_causal, seed, offset)
-        p.dout = dout.data_ptr()
-        p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
-        p.softmax_d = softmax_d.data_ptr()
-        p.dq_row_stride, p.dq_head_stride = dq.stride(0), dq.stride(1)
-        p.dk_row_stride, p.dk_head_stride = dk.stride(0), dk.stride(1)
-        p.dv_row_stride, p.dv_head_stride = dv.stride(0), dv.stride(1)
+        nbytes = lib.fa_bwd_workspace_bytes(total_q, heads, d)
+        ws = _workspace(q.device, nbytes)
+        dqs, dks, dvs = dq.stride(), dk.stride(), dv.stride()
+        p = BwdParams(_make_fwd((batch, total_q, total_k, heads, d), q, k, v, out, softmax_lse,
+                                cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout,
+                                softmax_scale, is_causal, seed, offset),
+                      dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), softmax_d.data_ptr(),
+                      dqs[0], dqs[1], dks[0], dks[1], dvs[0], dvs[1], ws.data_ptr(), ws.numel(),
+                      _stage_mask)
         if _blockmask is not None:
             _require(not is_causal, "block-sparse attention does not support causal")
             _check_blockmask(_blockmask, max_seqlen_q, max_seqlen_k, q)
@@ -290,11 +300,6 @@ def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
             p.fwd.blockmask = _blockmask.data_ptr()
             p.fwd.blockmask_rows, p.fwd.blockmask_cols = _blockmask.shape
             p.fwd.bs_workspace, p.fwd.bs_workspace_bytes = bws.data_ptr(), bws.numel()
-        nbytes = lib.fa_bwd_workspace_bytes(total_q, heads, d)
-        ws = _workspace(q.device, nbytes)
-        p.workspace = ws.data_ptr()
-        p.workspace_bytes = ws.numel()
-        p.stage_mask = _stage_mask
         check(lib.fa_bwd(ctypes.byref(p), _raw_stream()))
     return [dq, dk, dv, softmax_d]
 
