@@ -608,6 +608,32 @@ def extras(fc, dev, peaks, only=None):
             "scatter_frac_hbm_peak": scatter_bytes / t[1] / 1e6 / peaks["hbm_gbs"],
             "torch_index_select_ms": t[2], "torch_zeros_index_copy_ms": t[3]}
         del x, packed
+    # rotary embedding on packed qkv (HBM bound): one pass, qkv read once and written once
+    if wanted("rotary_qkv_fp16_B64_S512_H12_D64"):
+        from flash_attn_b200.rotary import RotaryEmbedding
+        B, S, H, D = 64, 512, 12, 64
+        qkv = torch.randn(B, S, 3, H, D, device=dev, dtype=torch.float16, generator=g)
+        rope = RotaryEmbedding(D).to(dev)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        for it in range(2):
+            if it == 1:
+                torch.cuda.synchronize()
+                ev[0].record()
+            for _ in range(5):
+                rope.apply_qkv(qkv)
+            if it == 1:
+                ev[1].record()
+            for _ in range(5):
+                q_, k_ = rope(qkv[:, :, 0], qkv[:, :, 1], seq_dimension=-3)
+                torch.stack([q_, k_, qkv[:, :, 2]], dim=2)
+        ev[2].record()
+        torch.cuda.synchronize()
+        t_fused, t_ops = ev[0].elapsed_time(ev[1]) / 5, ev[1].elapsed_time(ev[2]) / 5
+        nbytes = 2 * qkv.numel() * 2
+        res["rotary_qkv_fp16_B64_S512_H12_D64"] = {
+            "fused_ms": t_fused, "fused_gbs": nbytes / t_fused / 1e6,
+            "fused_frac_hbm_peak": nbytes / t_fused / 1e6 / peaks["hbm_gbs"], "framework_ops_ms": t_ops}
+        del qkv
     # long context, one GPU's share of an 8-way head shard (batch 2, 32 / 8 = 4 heads, d = 64, causal, bf16)
     if wanted("long_context_bf16_d64_S65536_4heads"):
         B, H, d, S = 2, 4, 64, 65536

@@ -220,6 +220,23 @@ int fa_scatter_rows(const void* src, const int64_t* indices, void* dst, int64_t 
   return FA_OK;
 }
 
+int fa_rotary_qkv(const void* qkv, void* out, const float* cos_table, const float* sin_table,
+                  int64_t rows, int32_t seqlen, int32_t heads, int32_t head_dim, int32_t is_bf16,
+                  int32_t conjugate, void* cuda_stream) {
+  FA_REQUIRE(rows >= 0 && seqlen > 0 && heads > 0 && head_dim > 0, "sizes must be positive");
+  if (rows == 0) return FA_OK;
+  FA_REQUIRE(qkv && out && cos_table && sin_table, "null pointer");
+  FA_REQUIRE(qkv != out, "out may not alias qkv");
+  FA_REQUIRE(head_dim % 8 == 0, "head_dim must be a multiple of 8");
+  FA_REQUIRE(rows % seqlen == 0, "rows must be a multiple of seqlen");
+  FA_REQUIRE(((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(out) |
+               reinterpret_cast<uintptr_t>(cos_table) | reinterpret_cast<uintptr_t>(sin_table)) & 15) == 0,
+             "qkv, out and the tables must be 16-byte aligned");
+  FA_CUDA(fa::launch_rotary_qkv(qkv, out, cos_table, sin_table, rows, seqlen, heads, head_dim,
+                                is_bf16 != 0, conjugate != 0, static_cast<cudaStream_t>(cuda_stream)));
+  return FA_OK;
+}
+
 const char* fa_status_string(int status) {
   switch (status) {
     case FA_OK: return "ok";

@@ -81,6 +81,10 @@ cudaError_t launch_scatter_rows(const void* src, const int64_t* indices, void* d
                                 int64_t n_dst_rows, int64_t row_bytes, int32_t* inverse,
                                 cudaStream_t stream);
 
+cudaError_t launch_rotary_qkv(const void* qkv, void* out, const float* cos_t, const float* sin_t,
+                              int64_t rows, int seqlen, int heads, int d, bool bf16, bool conj,
+                              cudaStream_t stream);
+
 // Raises the dynamic shared-memory limit of `kernel` the first time it is launched on a device
 // (the attribute belongs to the device's context; setting it on every launch costs microseconds).
 // `done` is the caller's per-kernel flag array, one entry per device: kernels that differ only in

@@ -28,6 +28,7 @@ EXPORTED_SYMBOLS = (
     "fa_debug_philox",
     "fa_gather_rows",
     "fa_scatter_rows",
+    "fa_rotary_qkv",
     "fa_status_string",
     "fa_last_error",
     "fa_device_supported",
@@ -134,6 +135,10 @@ def _load():
     lib.fa_scatter_rows.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
                                     ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
     lib.fa_scatter_rows.restype = ctypes.c_int
+    lib.fa_rotary_qkv.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                  ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                  ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
+    lib.fa_rotary_qkv.restype = ctypes.c_int
     lib.fa_status_string.argtypes = [ctypes.c_int]
     lib.fa_status_string.restype = ctypes.c_char_p
     lib.fa_last_error.argtypes = []

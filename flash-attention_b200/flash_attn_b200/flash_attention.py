@@ -91,7 +91,9 @@ class FlashMHA(nn.Module):
                 need_weights=False):
         batch, seqlen, _ = x.shape
         qkv = self.Wqkv(x).reshape(batch, seqlen, 3, self.num_heads, self.head_dim)
-        if self.use_rotary_emb:
+        if self.use_rotary_emb == "1d":
+            qkv = self.rotary_emb.apply_qkv(qkv)   # one pass over qkv on CUDA
+        elif self.use_rotary_emb:
             q, k, v = qkv.unbind(dim=2)
             q, k = self.rotary_emb(q, k, seq_dimension=-3)
             qkv = torch.stack([q, k, v], dim=2)

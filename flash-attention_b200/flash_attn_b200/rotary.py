@@ -1,9 +1,12 @@
 """Rotary position embeddings used by FlashMHA(use_rotary_emb=...): same results as
 flash_attn/rotary.py in the reference (consecutive channel pairs (2i, 2i+1) are rotated by
 position * 10000^(-2i/dim)), written as a complex multiplication."""
+import ctypes
 import math
 
 import torch
+
+from ._lib import check, lib
 
 
 def _rotate(x, angles):
@@ -11,6 +14,32 @@ def _rotate(x, angles):
     xc = torch.view_as_complex(x.float().reshape(*x.shape[:-1], -1, 2))
     rot = torch.polar(torch.ones_like(angles), angles)
     return torch.view_as_real(xc * rot).flatten(-2).to(x.dtype)
+
+
+class _RotaryQKV(torch.autograd.Function):
+    """Rotation of the q and k parts of a packed (batch, seqlen, 3, heads, d) tensor by the library's
+    one-pass kernel (fa_rotary_qkv); the gradient is the rotation by the negative angles."""
+
+    @staticmethod
+    def _run(qkv, cos, sin, conjugate):
+        batch, seqlen, _, heads, d = qkv.shape
+        out = torch.empty_like(qkv)
+        with torch.cuda.device(qkv.device):
+            stream = ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(qkv.device.index))
+            check(lib.fa_rotary_qkv(qkv.data_ptr(), out.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                    batch * seqlen, seqlen, heads, d,
+                                    1 if qkv.dtype is torch.bfloat16 else 0, 1 if conjugate else 0, stream))
+        return out
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin):
+        ctx.save_for_backward(cos, sin)
+        return _RotaryQKV._run(qkv, cos, sin, False)
+
+    @staticmethod
+    def backward(ctx, grad):
+        cos, sin = ctx.saved_tensors
+        return _RotaryQKV._run(grad.contiguous(), cos, sin, True), None, None
 
 
 class RotaryEmbedding(torch.nn.Module):
@@ -30,6 +59,32 @@ class RotaryEmbedding(torch.nn.Module):
         assert seq_dimension in (-2, -3)
         ang = self._angles(k, seq_dimension)
         return (_rotate(q, ang[:q.shape[seq_dimension]]), _rotate(k, ang))
+
+    @staticmethod
+    def fused_path(qkv):
+        """The one-pass kernel takes a contiguous 16-bit CUDA tensor (batch, seqlen, 3, heads, d) with
+        d a multiple of 8."""
+        return (qkv.is_cuda and qkv.dim() == 5 and qkv.shape[2] == 3 and qkv.is_contiguous()
+                and qkv.dtype in (torch.float16, torch.bfloat16) and qkv.shape[-1] % 8 == 0
+                and qkv.data_ptr() % 16 == 0)
+
+    def apply_qkv(self, qkv):
+        """(batch, seqlen, 3, heads, d) -> the same layout with q and k rotated, v unchanged: what
+        forward(q, k, seq_dimension=-3) followed by a re-stack computes, in one pass over qkv."""
+        if not self.fused_path(qkv):
+            q, k, v = qkv.unbind(dim=2)
+            q, k = self.forward(q, k, seq_dimension=-3)
+            return torch.stack([q, k, v], dim=2)
+        seqlen = qkv.shape[1]
+        key = (seqlen, qkv.device)
+        if getattr(self, "_table_key", None) != key:
+            # fp32 tables, kept until the sequence length or the device changes (the reference
+            # caches its tables the same way, flash_attn/rotary.py:72-88)
+            t = torch.arange(seqlen, device=qkv.device, dtype=self.inv_freq.dtype)
+            ang = torch.outer(t, self.inv_freq.to(qkv.device))        # (seqlen, d / 2)
+            self._cos_table, self._sin_table = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+            self._table_key = key
+        return _RotaryQKV.apply(qkv, self._cos_table, self._sin_table)
 
 
 class RotaryEmbedding2D(torch.nn.Module):

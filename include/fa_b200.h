@@ -185,6 +185,17 @@ int fa_gather_rows(const void* src, const int64_t* indices, void* dst, int64_t n
 int fa_scatter_rows(const void* src, const int64_t* indices, void* dst, int64_t n_src_rows,
                     int64_t n_dst_rows, int64_t row_bytes, int32_t* workspace, void* cuda_stream);
 
+/* Rotary position embedding on a packed qkv tensor (rows, 3, heads, head_dim), rows = batch *
+ * seqlen with the token position = row % seqlen: q and k are rotated pairwise (channels 2i, 2i+1 by
+ * the angle with cosine cos_table[pos][i] and sine sin_table[pos][i], fp32 tables of head_dim / 2
+ * entries per position), v is copied; `out` has the layout of `qkv` and may not alias it.
+ * Replaces flash_attn/rotary.py:33-43 (apply_rotary_pos_emb on q and k) plus the re-stack in
+ * flash_attn/flash_attention.py:102-105.  conjugate != 0 rotates by the negative angles (the
+ * gradient).  head_dim must be a multiple of 8; qkv and out 16-byte aligned and contiguous. */
+int fa_rotary_qkv(const void* qkv, void* out, const float* cos_table, const float* sin_table,
+                  int64_t rows, int32_t seqlen, int32_t heads, int32_t head_dim, int32_t is_bf16,
+                  int32_t conjugate, void* cuda_stream);
+
 const char* fa_status_string(int status);
 const char* fa_last_error(void);
 
