@@ -111,24 +111,30 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_attention_sample(seqlen, heads, d, causal, threads, repeats=1):
-    """fwd+bwd of the oracle's standard attention (fp32) for one sequence of `seqlen` tokens;
-    returns (seconds per pass, flops per pass)."""
+def cpu_attention_sample(seqlen, heads, d, causal, threads, repeats=1, min_seconds=0.0):
+    """fwd+bwd of the oracle's standard attention (fp32) for one sequence of `seqlen` tokens, run
+    `repeats` times after a warm-up pass and then until `min_seconds` of timed work have been done;
+    returns (mean seconds per pass, flops per pass, passes timed)."""
     from oracle import attention_oracle as orc
     torch.set_num_threads(threads)
     g = torch.Generator().manual_seed(0)
     qkv = torch.randn(1, seqlen, 3, heads, d, generator=g, requires_grad=True)
     dout = torch.randn(1, seqlen, heads, d, generator=g)
     mask = torch.ones(1, seqlen, dtype=torch.bool)
-    best = float("inf")
-    for _ in range(repeats + 1):  # first pass is the warm-up
+
+    def one_pass():
         qkv.grad = None
         t0 = time.perf_counter()
         out = orc.attention_ref(qkv, mask, 0.0, upcast=True, causal=causal)
         out.backward(dout)
-        dt = time.perf_counter() - t0
-        best = min(best, dt) if _ > 0 else best
-    return best, 3.5 * fwd_flops([seqlen], heads, d, causal)
+        return time.perf_counter() - t0
+
+    one_pass()  # warm-up
+    total, n = 0.0, 0
+    while n < repeats or (total < min_seconds and n < 400):
+        total += one_pass()
+        n += 1
+    return total / n, 3.5 * fwd_flops([seqlen], heads, d, causal), n
 
 
 def run_reference(args):
@@ -144,12 +150,13 @@ def run_reference(args):
     times = []
     flops = 0.0
     for i in range(args.warmup + args.steps):
-        dt, flops = cpu_attention_sample(sample_len, HEADS, HEAD_DIM, False, threads, repeats=1)
+        dt, flops, _ = cpu_attention_sample(sample_len, HEADS, HEAD_DIM, False, threads, repeats=4)
         if i >= args.warmup:
             times.append(dt)
     t = float(np.mean(times))
     value = flops / t / 1e12
-    sample = "1 sequence of %d tokens x %d heads, dropout off, fp32 standard attention" % (sample_len, HEADS)
+    sample = ("each step: 4 passes over 1 sequence of %d tokens x %d heads, dropout off, fp32 standard "
+              "attention fwd+bwd" % (sample_len, HEADS))
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
@@ -404,11 +411,12 @@ def main():
     if rank == 0 and world == 1 and not args.kernels_only:
         threads = os.cpu_count() or 1
         sample_len = min(max(lengths), 2048)
-        dt, fl = cpu_attention_sample(sample_len, HEADS, HEAD_DIM, False, threads, repeats=2)
+        dt, fl, passes = cpu_attention_sample(sample_len, HEADS, HEAD_DIM, False, threads, repeats=2,
+                                              min_seconds=10.0)
         line["cpu_baseline"] = {
             "value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-            "sample": "1 sequence of %d tokens x %d heads, fp32 standard attention fwd+bwd, dropout off"
-                      % (sample_len, HEADS)}
+            "sample": "%d passes (about 10 s) over 1 sequence of %d tokens x %d heads, fp32 standard "
+                      "attention fwd+bwd, dropout off" % (passes, sample_len, HEADS)}
         if not args.no_extras:
             line["extras"] = extras(fc, dev, peaks)
     if rank == 0:
