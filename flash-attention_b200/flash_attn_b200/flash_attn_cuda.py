@@ -106,32 +106,6 @@ def _check_qkv(q, k, v, cu_seqlens_q, cu_seqlens_k):
     return batch, total_q, total_k, heads, d
 
 
-def _fill_fwd(p, dims, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout, scale, causal,
-              seed, offset):
-    batch, total_q, total_k, heads, d = dims
-    p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
-    p.o = o.data_ptr()
-    p.softmax_lse = lse.data_ptr()
-    p.cu_seqlens_q, p.cu_seqlens_k = cu_q.data_ptr(), cu_k.data_ptr()
-    p.blockmask = None
-    p.s_dmask = None
-    p.q_row_stride, p.q_head_stride = q.stride(0), q.stride(1)
-    p.k_row_stride, p.k_head_stride = k.stride(0), k.stride(1)
-    p.v_row_stride, p.v_head_stride = v.stride(0), v.stride(1)
-    p.o_row_stride, p.o_head_stride = o.stride(0), o.stride(1)
-    p.lse_stride = lse.shape[-1]
-    p.batch, p.heads, p.head_dim = batch, heads, d
-    p.total_q, p.total_k = total_q, total_k
-    p.max_seqlen_q, p.max_seqlen_k = int(max_q), int(max_k)
-    p.p_dropout = float(p_dropout)
-    p.softmax_scale = float(scale)
-    p.is_causal = int(bool(causal))
-    p.is_bf16 = int(q.dtype == torch.bfloat16)
-    p.philox_seed, p.philox_offset = seed, offset
-    p.mask_heads_total, p.mask_head_offset = 0, 0
-    p.status = _status_buffer(q.device).data_ptr()
-
-
 def _make_fwd(dims, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout, scale, causal, seed, offset):
     """FwdParams filled through the structure's positional constructor (one call instead of forty
     attribute stores): the per-call host time of short-sequence workloads is mostly this binding."""
@@ -144,6 +118,12 @@ def _make_fwd(dims, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout, scale,
                      float(p_dropout), float(scale), 1 if causal else 0,
                      1 if q.dtype is torch.bfloat16 else 0, seed, offset, 0, 0,
                      _status_buffer(q.device).data_ptr(), None, 0, 0, 0)
+
+
+def _fill_fwd(p, dims, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout, scale, causal, seed, offset):
+    """Same as _make_fwd, into an existing FwdParams (for instance the `fwd` member of a BwdParams)."""
+    src = _make_fwd(dims, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout, scale, causal, seed, offset)
+    ctypes.memmove(ctypes.addressof(p), ctypes.addressof(src), ctypes.sizeof(FwdParams))
 
 
 def _round_up(x, m):
