@@ -196,3 +196,39 @@ def test_full_size_properties(batch, heads, d, seqlen, causal, dtype):
     torch.cuda.synchronize()
     fc.check_device_status()
     assert (o12.float() - (0.5 * o1.float() + 0.25 * o2.float())).abs().max().item() < 3e-2
+
+
+@pytest.mark.parametrize("d,dtype,causal,gain", [
+    (64, torch.float16, False, 6.0),
+    (64, torch.bfloat16, True, 8.0),
+    (128, torch.bfloat16, False, 5.0),
+])
+def test_large_scores_and_growing_maxima(d, dtype, causal, gain):
+    """Scores tens of units apart (peaked softmax rows) and keys sorted so that the row maximum keeps
+    growing from key tile to key tile: exercises the deferred rescaling of the running maximum (the
+    kernel keeps a stale maximum while it lags by less than 2^8) without overflow or loss."""
+    fc = _fc()
+    sq, sk, heads = [384, 200], [640, 257], 2
+    q, k, v, dout, cu_q, cu_k = U.make_varlen(sq, sk, heads, d, dtype, seed=77)
+    # later keys align more and more with a common direction of the queries
+    direction = torch.randn(d, device="cuda").to(dtype)
+    ramp = torch.cat([torch.linspace(0.0, 1.0, n, device="cuda") for n in sk]).to(dtype)
+    k = (k + gain * ramp[:, None, None] * direction[None, None, :]).contiguous()
+    q = (q + 0.5 * direction[None, None, :]).contiguous()
+    scale = 1.0 / math.sqrt(d)
+    out, lse = fc.fwd(q, k, v, cu_q, cu_k, max(sq), max(sk), 0.0, scale, False, causal, False, None)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    fc.bwd(dout, q, k, v, out, lse, dq, dk, dv, cu_q, cu_k, max(sq), max(sk), 0.0, scale, False, causal, None)
+    torch.cuda.synchronize()
+    fc.check_device_status()
+    for name, x in (("out", out), ("dq", dq), ("dk", dk), ("dv", dv), ("lse", lse)):
+        assert torch.isfinite(x.float()).all() or name == "lse", name
+    o32, dq32, dk32, dv32 = U.oracle_cpu(q, k, v, dout, cu_q, cu_k, scale, causal)
+    o16, dq16, dk16, dv16 = U.oracle_cpu(q, k, v, dout, cu_q, cu_k, scale, causal, dtype=dtype)
+    U.assert_within_2x("out", out, o32, o16)
+    U.assert_within_2x("dq", dq, dq32, dq16)
+    U.assert_within_2x("dk", dk, dk32, dk16)
+    U.assert_within_2x("dv", dv, dv32, dv16)
+    lses = U.oracle_lse(q, k, v, cu_q, cu_k, scale, causal)
+    for b, n in enumerate(sq):
+        assert U.max_err(lse[b, :, :n], lses[b]) < 2e-3   # LSE values reach the hundreds here
