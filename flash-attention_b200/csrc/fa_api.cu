@@ -53,14 +53,16 @@ EncodeTiledFn get_encode_tiled() {
 // 3-D map over a [rows, heads, head_dim] tensor with arbitrary row / head strides:
 // dim0 = head_dim, dim1 = rows, dim2 = heads; box = 64 columns x box_rows rows x 1 head, stored
 // with the 128-byte swizzle.  Columns beyond head_dim and rows beyond `rows` read as zero.
+// `bind_context`: a thread that has only used the runtime API lazily (an autograd worker, for
+// instance) may not have the primary context bound yet and the driver call below needs it;
+// cudaFree(nullptr) binds it.  The entry point that must not touch the allocator passes false
+// (it has bound the context with cudaSetDevice already).
 int make_tile_map(CUtensorMap* tm, const void* base, bool bf16, int64_t rows, int heads, int head_dim,
-                  int64_t row_stride, int64_t head_stride, int box_rows) {
+                  int64_t row_stride, int64_t head_stride, int box_rows, bool bind_context = true) {
   EncodeTiledFn enc = get_encode_tiled();
   if (!enc) return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  // A thread that has only used the runtime API lazily (an autograd worker, for instance) may not
-  // have the primary context bound yet; the driver call below needs it.
   static thread_local bool context_bound = false;
-  if (!context_bound) {
+  if (bind_context && !context_bound) {
     FA_CUDA(cudaFree(nullptr));
     context_bound = true;
   }
@@ -350,8 +352,11 @@ size_t fa_bwd_workspace_bytes(int32_t total_q, int32_t heads, int32_t head_dim) 
   return static_cast<size_t>(total_q) * static_cast<size_t>(heads) * dpad * sizeof(float);
 }
 
-int fa_bwd(const fa_bwd_params* p, void* cuda_stream) {
-  FA_REQUIRE(p != nullptr, "params is null");
+namespace {
+
+// Body shared by fa_bwd and fa_bwd_static_scratch: validation, kernel arguments, the five tensor
+// maps and the launches.  `accum` is the fp32 dQ accumulator (already checked to be large enough).
+int run_bwd(const fa_bwd_params* p, float* accum, int stage_mask, bool bind_context, cudaStream_t stream) {
   const fa_fwd_params* f = &p->fwd;
   if (int rc = validate_common(f)) return rc;
   FA_REQUIRE(f->o && f->softmax_lse, "out and softmax_lse must be non-null");
@@ -363,21 +368,19 @@ int fa_bwd(const fa_bwd_params* p, void* cuda_stream) {
                  p->dk_head_stride % 8 == 0 && p->dv_row_stride % 8 == 0 && p->dv_head_stride % 8 == 0 &&
                  f->o_row_stride % 8 == 0 && f->o_head_stride % 8 == 0,
              "gradient strides must be multiples of 8 elements");
-  const size_t need = fa_bwd_workspace_bytes(f->total_q, f->heads, f->head_dim);
-  if (p->workspace == nullptr || p->workspace_bytes < need)
-    return fail(FA_ERR_WORKSPACE, "workspace must hold " + std::to_string(need) + " bytes");
-  FA_REQUIRE((reinterpret_cast<uintptr_t>(p->workspace) & 15) == 0, "workspace must be 16-byte aligned");
+  FA_REQUIRE((reinterpret_cast<uintptr_t>(accum) & 15) == 0, "workspace must be 16-byte aligned");
 
   fa::BwdLaunch l;
   std::memset(&l, 0, sizeof(l));
   fill_args(f, &l.args.k);
   if (f->blockmask)
-    if (int rc = setup_blocksparse(f, &l.args.k, static_cast<cudaStream_t>(cuda_stream))) return rc;
+    if (int rc = setup_blocksparse(f, &l.args.k, stream)) return rc;
   l.dpad = f->head_dim <= 64 ? 64 : 128;
   l.is_bf16 = f->is_bf16 != 0;
   l.is_causal = f->is_causal != 0;
   l.is_dropout = f->p_dropout > 0.f;
-  l.stage_mask = p->stage_mask;
+  l.stage_mask = stage_mask;
+  l.deterministic = p->deterministic != 0;
   fa::BwdArgs& a = l.args;
   a.o_in = f->o;
   a.dout = p->dout;
@@ -388,21 +391,50 @@ int fa_bwd(const fa_bwd_params* p, void* cuda_stream) {
   a.dk_row_stride = p->dk_row_stride; a.dk_head_stride = p->dk_head_stride;
   a.dv_row_stride = p->dv_row_stride; a.dv_head_stride = p->dv_head_stride;
   a.softmax_d = p->softmax_d;
-  a.dq_accum = static_cast<float*>(p->workspace);
+  a.dq_accum = accum;
+  if (l.deterministic) {
+    // ticket words sit behind the accumulator (fa_bwd_workspace_bytes_ex)
+    const size_t off = fa_bwd_workspace_bytes(f->total_q, f->heads, f->head_dim);
+    a.dq_tickets = reinterpret_cast<int32_t*>(reinterpret_cast<char*>(accum) + ((off + 255) & ~size_t(255)));
+    a.ticket_stride = (f->max_seqlen_q + 127) / 128;
+  }
   a.total_q = f->total_q; a.total_k = f->total_k;
   a.max_seqlen_q = f->max_seqlen_q; a.max_seqlen_k = f->max_seqlen_k;
   a.p_keep = 1.f - f->p_dropout;
   if (int rc = make_tile_map(&l.tm_q, f->q, l.is_bf16, f->total_q, f->heads, f->head_dim,
-                             f->q_row_stride, f->q_head_stride, 128)) return rc;
+                             f->q_row_stride, f->q_head_stride, 128, bind_context)) return rc;
   if (int rc = make_tile_map(&l.tm_k, f->k, l.is_bf16, f->total_k, f->heads, f->head_dim,
-                             f->k_row_stride, f->k_head_stride, 128)) return rc;
+                             f->k_row_stride, f->k_head_stride, 128, bind_context)) return rc;
   if (int rc = make_tile_map(&l.tm_v, f->v, l.is_bf16, f->total_k, f->heads, f->head_dim,
-                             f->v_row_stride, f->v_head_stride, 128)) return rc;
+                             f->v_row_stride, f->v_head_stride, 128, bind_context)) return rc;
   if (int rc = make_tile_map(&l.tm_do, p->dout, l.is_bf16, f->total_q, f->heads, f->head_dim,
-                             a.do_row_stride, a.do_head_stride, 128)) return rc;
+                             a.do_row_stride, a.do_head_stride, 128, bind_context)) return rc;
   if (int rc = make_accum_map(&l.tm_dq, a.dq_accum, f->total_q, f->heads, l.dpad)) return rc;
-  FA_CUDA(fa::launch_bwd(l, static_cast<cudaStream_t>(cuda_stream)));
+  FA_CUDA(fa::launch_bwd(l, stream));
   return FA_OK;
+}
+
+}  // namespace
+
+size_t fa_bwd_workspace_bytes_ex(int32_t total_q, int32_t heads, int32_t head_dim, int32_t batch,
+                                 int32_t max_seqlen_q, int32_t deterministic) {
+  const size_t accum = fa_bwd_workspace_bytes(total_q, heads, head_dim);
+  if (!deterministic) return accum;
+  const size_t tickets = static_cast<size_t>(batch) * static_cast<size_t>(heads) *
+                         static_cast<size_t>((max_seqlen_q + 127) / 128) * sizeof(int32_t);
+  return ((accum + 255) & ~size_t(255)) + tickets;
+}
+
+int fa_bwd(const fa_bwd_params* p, void* cuda_stream) {
+  FA_REQUIRE(p != nullptr, "params is null");
+  const fa_fwd_params* f = &p->fwd;
+  FA_REQUIRE(f->total_q >= 0 && f->heads > 0 && f->batch > 0 && f->max_seqlen_q > 0, "bad sizes");
+  const size_t need = fa_bwd_workspace_bytes_ex(f->total_q, f->heads, f->head_dim, f->batch,
+                                                f->max_seqlen_q, p->deterministic);
+  if (p->workspace == nullptr || p->workspace_bytes < need)
+    return fail(FA_ERR_WORKSPACE, "workspace must hold " + std::to_string(need) + " bytes");
+  return run_bwd(p, static_cast<float*>(p->workspace), p->stage_mask, true,
+                 static_cast<cudaStream_t>(cuda_stream));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -443,44 +475,14 @@ int static_scratch_address(float** out) {
   return FA_OK;
 }
 
-// make_tile_map without the context-binding cudaFree (static_scratch_address already bound it).
-int encode_tile_map(CUtensorMap* tm, const void* base, bool bf16, int64_t rows, int heads, int head_dim,
-                    int64_t row_stride, int64_t head_stride) {
-  EncodeTiledFn enc = get_encode_tiled();
-  if (!enc) return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  FA_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "tensor base must be 16-byte aligned");
-  FA_REQUIRE((row_stride * 2) % 16 == 0 && (head_stride * 2) % 16 == 0,
-             "row and head strides must be multiples of 8 elements");
-  cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(rows),
-                        static_cast<cuuint64_t>(heads)};
-  cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_stride) * 2, static_cast<cuuint64_t>(head_stride) * 2};
-  cuuint32_t box[3] = {64, 128, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS)
-    return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
-  return FA_OK;
-}
-
 }  // namespace
 
 int fa_bwd_static_scratch(const fa_bwd_params* p, void* cuda_stream) {
   FA_REQUIRE(p != nullptr, "params is null");
   const fa_fwd_params* f = &p->fwd;
-  if (int rc = validate_common(f)) return rc;
-  FA_REQUIRE(f->o && f->softmax_lse, "out and softmax_lse must be non-null");
-  FA_REQUIRE(p->dout && p->dq && p->dk && p->dv && p->softmax_d, "dout, dq, dk, dv, softmax_d must be non-null");
-  FA_REQUIRE(((reinterpret_cast<uintptr_t>(p->dq) | reinterpret_cast<uintptr_t>(p->dk) |
-               reinterpret_cast<uintptr_t>(p->dv) | reinterpret_cast<uintptr_t>(f->o)) & 15) == 0,
-             "o, dq, dk, dv must be 16-byte aligned");
-  FA_REQUIRE(p->dq_row_stride % 8 == 0 && p->dq_head_stride % 8 == 0 && p->dk_row_stride % 8 == 0 &&
-                 p->dk_head_stride % 8 == 0 && p->dv_row_stride % 8 == 0 && p->dv_head_stride % 8 == 0 &&
-                 f->o_row_stride % 8 == 0 && f->o_head_stride % 8 == 0,
-             "gradient strides must be multiples of 8 elements");
-  const size_t need = fa_bwd_workspace_bytes(f->total_q, f->heads, f->head_dim);
+  FA_REQUIRE(f->total_q >= 0 && f->heads > 0 && f->batch > 0 && f->max_seqlen_q > 0, "bad sizes");
+  const size_t need = fa_bwd_workspace_bytes_ex(f->total_q, f->heads, f->head_dim, f->batch,
+                                                f->max_seqlen_q, p->deterministic);
   if (need > FA_STATIC_SCRATCH_BYTES)
     return fail(FA_ERR_WORKSPACE,
                 "fa_bwd_static_scratch: this call needs " + std::to_string(need) +
@@ -489,42 +491,8 @@ int fa_bwd_static_scratch(const fa_bwd_params* p, void* cuda_stream) {
                     " (total_q * heads * padded head_dim * 4); use fa_bwd with a workspace");
   float* accum = nullptr;
   if (int rc = static_scratch_address(&accum)) return rc;
-
-  fa::BwdLaunch l;
-  std::memset(&l, 0, sizeof(l));
-  fill_args(f, &l.args.k);
-  if (f->blockmask)
-    if (int rc = setup_blocksparse(f, &l.args.k, static_cast<cudaStream_t>(cuda_stream))) return rc;
-  l.dpad = f->head_dim <= 64 ? 64 : 128;
-  l.is_bf16 = f->is_bf16 != 0;
-  l.is_causal = f->is_causal != 0;
-  l.is_dropout = f->p_dropout > 0.f;
-  l.stage_mask = 0;  // all three stages: the preprocess stage clears the rows of the shared scratch it uses
-  fa::BwdArgs& a = l.args;
-  a.o_in = f->o;
-  a.dout = p->dout;
-  a.do_row_stride = static_cast<int64_t>(f->heads) * f->head_dim;
-  a.do_head_stride = f->head_dim;
-  a.dq = p->dq; a.dk = p->dk; a.dv = p->dv;
-  a.dq_row_stride = p->dq_row_stride; a.dq_head_stride = p->dq_head_stride;
-  a.dk_row_stride = p->dk_row_stride; a.dk_head_stride = p->dk_head_stride;
-  a.dv_row_stride = p->dv_row_stride; a.dv_head_stride = p->dv_head_stride;
-  a.softmax_d = p->softmax_d;
-  a.dq_accum = accum;
-  a.total_q = f->total_q; a.total_k = f->total_k;
-  a.max_seqlen_q = f->max_seqlen_q; a.max_seqlen_k = f->max_seqlen_k;
-  a.p_keep = 1.f - f->p_dropout;
-  if (int rc = encode_tile_map(&l.tm_q, f->q, l.is_bf16, f->total_q, f->heads, f->head_dim,
-                               f->q_row_stride, f->q_head_stride)) return rc;
-  if (int rc = encode_tile_map(&l.tm_k, f->k, l.is_bf16, f->total_k, f->heads, f->head_dim,
-                               f->k_row_stride, f->k_head_stride)) return rc;
-  if (int rc = encode_tile_map(&l.tm_v, f->v, l.is_bf16, f->total_k, f->heads, f->head_dim,
-                               f->v_row_stride, f->v_head_stride)) return rc;
-  if (int rc = encode_tile_map(&l.tm_do, p->dout, l.is_bf16, f->total_q, f->heads, f->head_dim,
-                               a.do_row_stride, a.do_head_stride)) return rc;
-  if (int rc = make_accum_map(&l.tm_dq, a.dq_accum, f->total_q, f->heads, l.dpad)) return rc;
-  FA_CUDA(fa::launch_bwd(l, static_cast<cudaStream_t>(cuda_stream)));
-  return FA_OK;
+  // all three stages: the preprocess stage clears the rows of the shared scratch this call uses
+  return run_bwd(p, accum, 0, false, static_cast<cudaStream_t>(cuda_stream));
 }
 
 }  // extern "C"

@@ -154,31 +154,54 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   int nm = m_tiles - m_begin;
   // block-sparse: query tiles that have at least one 16-row block in this key block's list
   __shared__ uint16_t qtile_list[BLOCKSPARSE ? kMaxSparseTiles : 1];
+  // deterministic mode: how many key tiles before this one add into the same query tile
+  __shared__ uint16_t qtile_order[BLOCKSPARSE ? kMaxSparseTiles : 1];
   __shared__ int qtile_count;
   if constexpr (BLOCKSPARSE) {
     uint8_t* flags = reinterpret_cast<uint8_t*>(smem_raw);
     const int32_t* brow = ka.bs_iter + (static_cast<int64_t>(b) * ka.bs_kblocks + (n0 >> 8)) * ka.bs_rows16;
     const int rb_end = min(ka.bs_rows16, (sq + 15) >> 4);
     const int mt = min(m_tiles, kMaxSparseTiles);
+    uint16_t* order_all = reinterpret_cast<uint16_t*>(smem_raw + kMaxSparseTiles);
     for (int m = threadIdx.x; m < mt; m += kBwdThreads) {
       bool any = false;
       for (int rb = m * (kBM / 16); rb < min((m + 1) * (kBM / 16), rb_end); ++rb) any = any || (brow[rb] >= 0);
       flags[m] = any ? 1 : 0;
+      if (a.dq_tickets != nullptr && any) {
+        // the two 128-row key tiles of a 256-row key block visit the same query tiles
+        int before = 0;
+        for (int kb = 0; kb < (n0 >> 8); ++kb) {
+          const int32_t* prow = ka.bs_iter + (static_cast<int64_t>(b) * ka.bs_kblocks + kb) * ka.bs_rows16;
+          bool hit = false;
+          for (int rb = m * (kBM / 16); rb < min((m + 1) * (kBM / 16), rb_end); ++rb) hit = hit || (prow[rb] >= 0);
+          before += hit ? 2 : 0;
+        }
+        order_all[m] = static_cast<uint16_t>(before + ((nt & 1) ? 1 : 0));
+      }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
       int n = 0;
       for (int m = 0; m < mt; ++m)
-        if (flags[m]) qtile_list[n++] = static_cast<uint16_t>(m);
+        if (flags[m]) {
+          if (a.dq_tickets != nullptr) qtile_order[n] = order_all[m];
+          qtile_list[n++] = static_cast<uint16_t>(m);
+        }
       qtile_count = n;
     }
     __syncthreads();
     nm = qtile_count;
     __syncthreads();
   }
+  // Deterministic mode: the key tiles of one (batch, head) add into a query tile in ascending
+  // key-tile order.  Dense causal grids then walk the query tiles from the last one down, so that
+  // every key tile starts on a query tile its predecessors start on too (walking up, key tile n
+  // would idle until tile n - 1 arrives at its first query tile).
+  const bool deterministic = a.dq_tickets != nullptr;
+  const bool walk_down = CAUSAL && !BLOCKSPARSE && deterministic;
   auto q_tile = [&](int t) -> int {
     if constexpr (BLOCKSPARSE) return qtile_list[t];
-    else return m_begin + t;
+    else return walk_down ? (m_tiles - 1 - t) : (m_begin + t);
   };
 
   uint16_t* dk_base = reinterpret_cast<uint16_t*>(a.dk);
@@ -789,6 +812,36 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       ++sync_phase;
       return done;
     };
+    // Deterministic mode (thread `row == 0` only): wait until the key tiles before this one have
+    // added their share of the query tile, add, wait for the adds to complete and pass the turn on.
+    int32_t* ticket_row = deterministic
+        ? a.dq_tickets + (static_cast<int64_t>(b) * ka.heads + h) * a.ticket_stride : nullptr;
+    auto ticket_wait = [&](int t) -> bool {
+      int32_t want;
+      if constexpr (BLOCKSPARSE) want = qtile_order[t];
+      else want = nt;
+      const volatile int32_t* tk = ticket_row + q_tile(t);
+      if (*abort_flag) return false;
+      const long long t0 = clock64();
+      while (true) {
+        int32_t cur;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(cur) : "l"(tk) : "memory");
+        if (cur >= want) break;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; return false; }
+      }
+      // the adds below go through the async proxy
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      return true;
+    };
+    bool my_turn = true;
+    auto ticket_pass = [&](int t) {
+      bulk_wait_all();
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      __threadfence();
+      int32_t* tk = ticket_row + q_tile(t);
+      asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(tk) : "memory");
+    };
     FA_PROF_DECL
     for (int t = 0; t < nm && ok; ++t) {
       const int m0 = q_tile(t) * kBM;
@@ -829,10 +882,16 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           if (row == 0) {
-            tma_reduce_add_3d(&tm_dq, stage_addr, half * 64, q_start + m0, h);
-            tma_reduce_add_3d(&tm_dq, stage_addr + 16384, half * 64 + 32, q_start + m0, h);
-            bulk_commit();
-            pending = true;
+            // on expiry the abort flag is set, this tile's add is skipped and every role leaves
+            // at its next wait
+            if (deterministic && half == 0) my_turn = ticket_wait(t);
+            if (my_turn) {
+              tma_reduce_add_3d(&tm_dq, stage_addr, half * 64, q_start + m0, h);
+              tma_reduce_add_3d(&tm_dq, stage_addr + 16384, half * 64 + 32, q_start + m0, h);
+              bulk_commit();
+              pending = true;
+              if (deterministic && half == D / 64 - 1) { ticket_pass(t); pending = false; }
+            }
           }
         }
 
@@ -868,10 +927,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         if (row == 0) {
-          tma_reduce_add_3d(&tm_dq, stage_addr, half * 64, q_start + m0, h);
-          tma_reduce_add_3d(&tm_dq, stage_addr + 16384, half * 64 + 32, q_start + m0, h);
-          bulk_commit();
-          pending = true;
+          if (deterministic && half == 0) my_turn = ticket_wait(t);
+          if (my_turn) {
+            tma_reduce_add_3d(&tm_dq, stage_addr, half * 64, q_start + m0, h);
+            tma_reduce_add_3d(&tm_dq, stage_addr + 16384, half * 64 + 32, q_start + m0, h);
+            bulk_commit();
+            pending = true;
+            if (deterministic && half == D / 64 - 1) { ticket_pass(t); pending = false; }
+          }
         }
       }
       }
@@ -906,6 +969,10 @@ __global__ void bwd_preprocess_kernel(const BwdArgs a, int dpad) {
   const int rows_per_block = blockDim.x / tpr;
   const int r = threadIdx.x / tpr, c = (threadIdx.x % tpr) * 8;
   const int i = blockIdx.x * rows_per_block + r;
+  if (a.dq_tickets != nullptr && blockIdx.x == 0) {
+    int32_t* tk = a.dq_tickets + (static_cast<int64_t>(b) * ka.heads + h) * a.ticket_stride;
+    for (int t = threadIdx.x; t < a.ticket_stride; t += blockDim.x) tk[t] = 0;
+  }
   float acc = 0.f;
   if (i < sq) {
     const int64_t row = q_start + i;
@@ -949,6 +1016,10 @@ __global__ void bwd_postprocess_kernel(const BwdArgs a, int dpad) {
   const int64_t rh = idx / tpr;
   const int h = static_cast<int>(rh % ka.heads);
   const int64_t row = rh / ka.heads;
+  // Rows behind the last sequence (a token buffer larger than cu_seqlens_q[batch]) belong to nobody:
+  // the accumulator was not cleared there and dq keeps what the caller put in it, as in the
+  // reference, which only ever writes rows of a sequence.
+  if (row >= ka.cu_seqlens_q[ka.batch]) return;
   const float* src = a.dq_accum + rh * dpad + c;
   const float4 x = *reinterpret_cast<const float4*>(src);
   const float4 y = *reinterpret_cast<const float4*>(src + 4);

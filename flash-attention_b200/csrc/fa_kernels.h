@@ -40,6 +40,10 @@ struct BwdArgs {
   int64_t dq_row_stride, dq_head_stride, dk_row_stride, dk_head_stride, dv_row_stride, dv_head_stride;
   float* softmax_d;
   float* dq_accum;    // fp32 [total_q, heads, Dpad]
+  // Deterministic mode: one ticket per (batch, head, 128-row query tile) = number of key tiles
+  // that have added their dQ tile so far; nullptr = add in arrival order.
+  int32_t* dq_tickets;
+  int32_t ticket_stride;  // tickets per (batch, head): ceil(max_seqlen_q / 128)
   int32_t total_q, total_k, max_seqlen_q, max_seqlen_k;
   float p_keep;
 };
@@ -59,6 +63,7 @@ struct BwdLaunch {
   bool is_bf16, is_causal, is_dropout;
   int32_t dpad;  // 64 or 128
   int32_t stage_mask;  // 0 = all; 1 preprocess, 2 main, 4 postprocess
+  bool deterministic;
 };
 
 cudaError_t launch_fwd(const FwdLaunch& l, cudaStream_t stream);

@@ -21,6 +21,7 @@ EXPORTED_SYMBOLS = (
     "fa_bwd",
     "fa_bwd_static_scratch",
     "fa_bwd_workspace_bytes",
+    "fa_bwd_workspace_bytes_ex",
     "fa_blocksparse_workspace_bytes",
     "fa_philox_increment",
     "fa_mask_block_n",
@@ -99,6 +100,7 @@ class BwdParams(ctypes.Structure):
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_size_t),
         ("stage_mask", ctypes.c_int32),
+        ("deterministic", ctypes.c_int32),
     ]
 
 
@@ -116,6 +118,8 @@ def _load():
     lib.fa_bwd_static_scratch.restype = ctypes.c_int
     lib.fa_bwd_workspace_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.fa_bwd_workspace_bytes.restype = ctypes.c_size_t
+    lib.fa_bwd_workspace_bytes_ex.argtypes = [ctypes.c_int32] * 6
+    lib.fa_bwd_workspace_bytes_ex.restype = ctypes.c_size_t
     lib.fa_blocksparse_workspace_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.fa_blocksparse_workspace_bytes.restype = ctypes.c_size_t
     lib.fa_philox_increment.argtypes = [ctypes.c_int32] * 4

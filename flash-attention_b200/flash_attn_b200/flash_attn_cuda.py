@@ -15,6 +15,44 @@ from ._lib import BwdParams, FwdParams, check, lib
 _status = {}
 
 
+class _Options:
+    """Process-wide switches of the binding that have no counterpart in the reference's argument
+    lists (the four entry points keep the reference's positional contract).
+
+    deterministic  backward passes add their dQ tiles in key-tile order, so dq is bit-for-bit
+                   reproducible (fa_bwd_params.deterministic); slower.
+    mask_heads     (heads_total, head_offset) or None: a rank that holds heads
+                   [head_offset, head_offset + heads) of a model with heads_total heads draws the
+                   dropout mask of the unsharded call (fa_fwd_params.mask_heads_total / _offset).
+    """
+    __slots__ = ("deterministic", "mask_heads")
+
+    def __init__(self):
+        self.deterministic = False
+        self.mask_heads = None
+
+
+options = _Options()
+
+
+class head_shard:
+    """Context manager: inside it every forward / backward on this process draws the dropout mask
+    of heads [head_offset, head_offset + heads) of an unsharded call with `heads_total` heads."""
+
+    def __init__(self, heads_total, head_offset):
+        self.value = (int(heads_total), int(head_offset))
+        self.prev = None
+
+    def __enter__(self):
+        self.prev = options.mask_heads
+        options.mask_heads = self.value
+        return self
+
+    def __exit__(self, *exc):
+        options.mask_heads = self.prev
+        return False
+
+
 def _status_buffer(device):
     """Per-device int32[4] the kernels write to when they abandon a bounded wait."""
     buf = _status.get(device)
@@ -111,12 +149,17 @@ def _make_fwd(dims, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout, scale,
     attribute stores): the per-call host time of short-sequence workloads is mostly this binding."""
     batch, total_q, total_k, heads, d = dims
     qs, ks, vs, os_ = q.stride(), k.stride(), v.stride(), o.stride()
+    mh = options.mask_heads
+    if mh is not None:
+        _require(mh[0] >= mh[1] + heads and mh[1] >= 0,
+                 "head_shard: heads_total must cover head_offset + heads of this call")
+    mh_total, mh_offset = mh if mh is not None else (0, 0)
     return FwdParams(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
                      cu_q.data_ptr(), cu_k.data_ptr(), None, None, 0, 0,
                      qs[0], qs[1], ks[0], ks[1], vs[0], vs[1], os_[0], os_[1], lse.shape[-1],
                      batch, heads, d, total_q, total_k, int(max_q), int(max_k),
                      float(p_dropout), float(scale), 1 if causal else 0,
-                     1 if q.dtype is torch.bfloat16 else 0, seed, offset, 0, 0,
+                     1 if q.dtype is torch.bfloat16 else 0, seed, offset, mh_total, mh_offset,
                      _status_buffer(q.device).data_ptr(), None, 0, 0, 0)
 
 
@@ -149,7 +192,8 @@ def _check_blockmask(blockmask, max_seqlen_q, max_seqlen_k, q):
 
 
 def _run_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout,
-             softmax_scale, zero_tensors, is_causal, return_softmax, gen, blockmask=None):
+             softmax_scale, zero_tensors, is_causal, return_softmax, gen, blockmask=None,
+             return_philox=False):
     batch, total_q, total_k, heads, d = _check_qkv(q, k, v, cu_seqlens_q, cu_seqlens_k)
     _require(p_dropout < 1.0, "p_dropout must be < 1")
     sparse = blockmask is not None
@@ -188,14 +232,24 @@ def _run_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_
             p.blockmask_rows, p.blockmask_cols = blockmask.shape
             p.bs_workspace, p.bs_workspace_bytes = ws.data_ptr(), ws.numel()
         check(lib.fa_fwd(ctypes.byref(p), _raw_stream()))
-    return [o, lse, s_dmask] if return_softmax else [o, lse]
+    res = [o, lse, s_dmask] if return_softmax else [o, lse]
+    if return_philox:
+        res += [seed, offset]
+    return res
 
 
 def fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale,
-        zero_tensors, is_causal, return_softmax, gen=None):
-    """mha_fwd (csrc/flash_attn/fmha_api.cpp:173-299): returns [o, softmax_lse(, s)]."""
+        zero_tensors, is_causal, return_softmax, gen=None, return_philox=False):
+    """mha_fwd (csrc/flash_attn/fmha_api.cpp:173-299): returns [o, softmax_lse(, s)].
+
+    return_philox (keyword, not in the reference): append the Philox (seed, offset) the dropout
+    mask of this call was drawn from -- the pair the reference takes from the generator under its
+    mutex (:288-292) and keeps to itself -- as two Python ints behind the tensors.  They are what
+    fa_fwd_params.philox_seed / philox_offset received; the generator has been advanced by
+    fa_philox_increment() past them.  Both are 0 when p_dropout == 0."""
     return _run_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout,
-                    softmax_scale, zero_tensors, is_causal, return_softmax, gen)
+                    softmax_scale, zero_tensors, is_causal, return_softmax, gen,
+                    return_philox=return_philox)
 
 
 def fwd_block(*args):
@@ -219,24 +273,15 @@ def fwd_block(*args):
     raise TypeError("fwd_block takes 9 or 13 positional arguments, got %d" % len(args))
 
 
-_workspaces = {}
-
-
-def _workspace(device, nbytes):
-    """Scratch for the fp32 dQ accumulator; grown on demand and reused by later calls on the same
-    device (calls on one device are ordered by the stream they run on)."""
-    ws = _workspaces.get(device)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
-        _workspaces[device] = ws
-    return ws
-
-
 def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
         max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, gen=None, _stage_mask=0,
-        _blockmask=None):
+        _blockmask=None, philox=None):
     """mha_bwd (csrc/flash_attn/fmha_api.cpp:302-449): writes dq, dk, dv in place and returns
-    [dq, dk, dv, softmax_d]."""
+    [dq, dk, dv, softmax_d].
+
+    philox (keyword, not in the reference): the (seed, offset) pair `fwd(..., return_philox=True)`
+    handed back; the mask is then regenerated from it and the generator is left alone (the
+    reference's callers restore the generator state around this call instead)."""
     batch, total_q, total_k, heads, d = _check_qkv(q, k, v, cu_seqlens_q, cu_seqlens_k)
     dt, qshape, kshape = q.dtype, q.shape, k.shape
     _require(dout.dtype is dt and out.dtype is dt, "dout / out dtype mismatch")
@@ -263,16 +308,20 @@ def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
             # The caller restores the generator state saved before the forward, so reading the
             # state here yields the forward's (seed, offset); the reference then advances it by a
             # dummy amount (csrc/flash_attn/fmha_api.cpp:437-445).
-            seed, offset = _philox_state(gen, 4)
-        nbytes = lib.fa_bwd_workspace_bytes(total_q, heads, d)
-        ws = _workspace(q.device, nbytes)
+            seed, offset = philox if philox is not None else _philox_state(gen, 4)
+        # fp32 dQ accumulator (and the ticket words of the deterministic mode): allocated per call
+        # from the caching allocator like the reference's dq_tmp (csrc/flash_attn/fmha_api.cpp:
+        # 402-404), so backward passes on different streams or threads never share scratch
+        det = 1 if options.deterministic else 0
+        nbytes = lib.fa_bwd_workspace_bytes_ex(total_q, heads, d, batch, int(max_seqlen_q), det)
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
         dqs, dks, dvs = dq.stride(), dk.stride(), dv.stride()
         p = BwdParams(_make_fwd((batch, total_q, total_k, heads, d), q, k, v, out, softmax_lse,
                                 cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout,
                                 softmax_scale, is_causal, seed, offset),
                       dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), softmax_d.data_ptr(),
                       dqs[0], dqs[1], dks[0], dks[1], dvs[0], dvs[1], ws.data_ptr(), ws.numel(),
-                      _stage_mask)
+                      _stage_mask, det)
         if _blockmask is not None:
             _require(not is_causal, "block-sparse attention does not support causal")
             _check_blockmask(_blockmask, max_seqlen_q, max_seqlen_k, q)

@@ -105,6 +105,12 @@ typedef struct fa_bwd_params {
   /* Profiling aid: which of the three backward launches to run.  0 = all; otherwise a bit mask,
    * 1 = preprocess (softmax_d, accumulator clear), 2 = main kernel, 4 = postprocess (dq write). */
   int32_t stage_mask;
+  /* Non-zero: dq is bit-for-bit reproducible from run to run, like the reference's, which adds the
+   * key blocks into dq_tmp one after the other (csrc/flash_attn/src/fmha_dgrad_kernel_1xN_loop.h:
+   * 523-595).  The key-tile CTAs then add their dQ tiles into the accumulator in ascending key-tile
+   * order through one ticket word per (batch, head, 128-row query tile) instead of in arrival
+   * order; the workspace must hold fa_bwd_workspace_bytes_ex(..., 1).  Slower: see the bench. */
+  int32_t deterministic;
 } fa_bwd_params;
 
 /* mha_fwd (csrc/flash_attn/fmha_api.cpp:173-299) and, with blockmask != NULL, mha_fwd_block
@@ -138,6 +144,11 @@ int fa_bwd_static_scratch(const fa_bwd_params* params, void* cuda_stream);
 /* Size of the scratch fa_bwd needs: replaces the dq_tmp allocation of mha_bwd
  * (csrc/flash_attn/fmha_api.cpp:402-404). */
 size_t fa_bwd_workspace_bytes(int32_t total_q, int32_t heads, int32_t head_dim);
+
+/* The same with the ticket words of the deterministic mode behind the accumulator when
+ * `deterministic` is non-zero (equal to fa_bwd_workspace_bytes otherwise). */
+size_t fa_bwd_workspace_bytes_ex(int32_t total_q, int32_t heads, int32_t head_dim, int32_t batch,
+                                 int32_t max_seqlen_q, int32_t deterministic);
 
 /* Scratch a block-sparse call needs (fa_fwd_params.bs_workspace): one int32 per (batch entry,
  * blockmask row, blockmask column).  The reference keeps this walk implicit in its kernels
