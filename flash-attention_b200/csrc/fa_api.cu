@@ -125,7 +125,6 @@ int validate_common(const fa_fwd_params* p) {
   FA_REQUIRE(p->p_dropout >= 0.f && p->p_dropout < 1.f, "p_dropout must be in [0, 1)");
   FA_REQUIRE(p->lse_stride >= p->max_seqlen_q, "softmax_lse rows are shorter than max_seqlen_q");
   if (p->blockmask) {
-    FA_REQUIRE(!p->is_causal, "block-sparse attention does not support the causal flag");
     FA_REQUIRE(!p->is_bf16, "block-sparse attention is fp16 only");
     FA_REQUIRE(p->head_dim <= 64, "block-sparse attention supports head_dim 16, 32, 64");
   }

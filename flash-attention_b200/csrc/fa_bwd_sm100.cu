@@ -166,6 +166,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     for (int m = threadIdx.x; m < mt; m += kBwdThreads) {
       bool any = false;
       for (int rb = m * (kBM / 16); rb < min((m + 1) * (kBM / 16), rb_end); ++rb) any = any || (brow[rb] >= 0);
+      if (CAUSAL && m < m_begin) any = false;  // query tiles entirely before this key tile see none of it
       flags[m] = any ? 1 : 0;
       if (a.dq_tickets != nullptr && any) {
         // the two 128-row key tiles of a 256-row key block visit the same query tiles
@@ -1080,9 +1081,13 @@ cudaError_t launch_bwd(const BwdLaunch& l, cudaStream_t stream) {
   if (stages & 2) {
     cudaError_t e;
     if (a.k.bs_iter != nullptr) {
-      // block-sparse exists for fp16, head_dim <= 64, non-causal only (checked by the C ABI)
-      e = l.is_dropout ? launch_main<64, false, false, true, true>(l, stream)
-                       : launch_main<64, false, false, false, true>(l, stream);
+      // block-sparse exists for fp16 and head_dim <= 64 (checked by the C ABI)
+      if (l.is_causal)
+        e = l.is_dropout ? launch_main<64, false, true, true, true>(l, stream)
+                         : launch_main<64, false, true, false, true>(l, stream);
+      else
+        e = l.is_dropout ? launch_main<64, false, false, true, true>(l, stream)
+                         : launch_main<64, false, false, false, true>(l, stream);
     } else {
       e = l.dpad == 64 ? launch_d<64>(l, stream) : launch_d<128>(l, stream);
     }

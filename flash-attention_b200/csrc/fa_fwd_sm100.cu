@@ -128,6 +128,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const int32_t* row = a.bs_iter + (static_cast<int64_t>(b) * a.bs_kblocks + (j >> 1)) * a.bs_rows16;
       bool any = false;
       for (int rb = rb0; rb < rb1; ++rb) any = any || (row[rb] >= 0);
+      // causal: a key tile that starts behind the CTA's last query row is masked entirely
+      if (CAUSAL && j * kBlockN > mp * 2 * kBlockM + 2 * kBlockM - 1) any = false;
       flags[j] = any ? 1 : 0;
     }
     __syncthreads();
@@ -151,7 +153,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     m0[g] = (mp * 2 + g) * kBlockM;
     const bool active = m0[g] < sq;
     int n = n_kv_total;
-    if (CAUSAL) n = min(n, m0[g] / kBlockN + 1);
+    if constexpr (CAUSAL && BLOCKSPARSE) {
+      // listed key tiles (ascending) up to the one that holds this query tile's diagonal
+      n = 0;
+      while (n < n_kv_total && tile_list[n] <= m0[g] / kBlockN) ++n;
+    } else if (CAUSAL) {
+      n = min(n, m0[g] / kBlockN + 1);
+    }
     n_tiles[g] = active ? n : 0;
   }
   const int n_max = max(n_tiles[0], n_tiles[1]);
@@ -608,7 +616,10 @@ cudaError_t launch_d(const FwdLaunch& l, cudaStream_t stream) {
 
 cudaError_t launch_fwd(const FwdLaunch& l, cudaStream_t stream) {
   if (l.args.bs_iter != nullptr) {
-    // block-sparse exists for fp16, head_dim <= 64, non-causal only (checked by the C ABI)
+    // block-sparse exists for fp16 and head_dim <= 64 (checked by the C ABI)
+    if (l.is_causal)
+      return l.is_dropout ? launch_one<64, false, true, true, true>(l, stream)
+                          : launch_one<64, false, true, false, true>(l, stream);
     return l.is_dropout ? launch_one<64, false, false, true, true>(l, stream)
                         : launch_one<64, false, false, false, true>(l, stream);
   }

@@ -91,12 +91,8 @@ class FlashMHA(nn.Module):
                 need_weights=False):
         batch, seqlen, _ = x.shape
         qkv = self.Wqkv(x).reshape(batch, seqlen, 3, self.num_heads, self.head_dim)
-        if self.use_rotary_emb == "1d":
-            qkv = self.rotary_emb.apply_qkv(qkv)   # one pass over qkv on CUDA
-        elif self.use_rotary_emb:
-            q, k, v = qkv.unbind(dim=2)
-            q, k = self.rotary_emb(q, k, seq_dimension=-3)
-            qkv = torch.stack([q, k, v], dim=2)
+        if self.use_rotary_emb:
+            qkv = self.rotary_emb.apply_qkv(qkv)   # one pass over qkv on CUDA, 1-D or 2-D angle table
         context, attn_weights = self.inner_attn(qkv, key_padding_mask=key_padding_mask,
                                                 need_weights=need_weights, causal=self.causal)
         return self.out_proj(context.reshape(batch, seqlen, self.embed_dim)), attn_weights

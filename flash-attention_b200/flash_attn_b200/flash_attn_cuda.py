@@ -198,7 +198,6 @@ def _run_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_
     _require(p_dropout < 1.0, "p_dropout must be < 1")
     sparse = blockmask is not None
     if sparse:
-        _require(not is_causal, "block-sparse attention does not support causal")
         _check_blockmask(blockmask, max_seqlen_q, max_seqlen_k, q)
     with _on_device(q.device):
         lse_len = _round_up(int(max_seqlen_q), 16)
@@ -252,7 +251,7 @@ def fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropo
                     return_philox=return_philox)
 
 
-def fwd_block(*args):
+def fwd_block(*args, return_philox=False):
     """mha_fwd_block.  Two call forms are accepted because the reference's Python call site and its
     C++ signature disagree:
       * 13 arguments, the C++ signature (csrc/flash_attn/fmha_api.cpp:451-464):
@@ -264,13 +263,16 @@ def fwd_block(*args):
     if len(args) == 13:
         (q, k, v, cu_q, cu_k, blockmask, max_q, max_k, p_dropout, scale, causal, ret_sm, gen) = args
         return _run_fwd(q, k, v, cu_q, cu_k, max_q, max_k, p_dropout, scale, False, causal, ret_sm,
-                        gen, blockmask=blockmask)
+                        gen, blockmask=blockmask, return_philox=return_philox)
     if len(args) == 9:
         (qkv, cu, blockmask, p_dropout, max_s, scale, causal, ret_sm, gen) = args
         _require(qkv.dim() == 4 and qkv.shape[1] == 3, "qkv must be (total, 3, heads, head_dim)")
         return _run_fwd(qkv[:, 0], qkv[:, 1], qkv[:, 2], cu, cu, max_s, max_s, p_dropout, scale,
-                        False, causal, ret_sm, gen, blockmask=blockmask)
+                        False, causal, ret_sm, gen, blockmask=blockmask, return_philox=return_philox)
     raise TypeError("fwd_block takes 9 or 13 positional arguments, got %d" % len(args))
+
+
+fwd_block.accepted_arities = (9, 13)
 
 
 def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
@@ -323,7 +325,6 @@ def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
                       dqs[0], dqs[1], dks[0], dks[1], dvs[0], dvs[1], ws.data_ptr(), ws.numel(),
                       _stage_mask, det)
         if _blockmask is not None:
-            _require(not is_causal, "block-sparse attention does not support causal")
             _check_blockmask(_blockmask, max_seqlen_q, max_seqlen_k, q)
             bws = _bs_workspace(q.device, batch, _blockmask)
             p.fwd.blockmask = _blockmask.data_ptr()
@@ -333,7 +334,7 @@ def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
     return [dq, dk, dv, softmax_d]
 
 
-def bwd_block(*args):
+def bwd_block(*args, philox=None):
     """mha_bwd_block.  Accepts the C++ signature (18 arguments,
     csrc/flash_attn/fmha_api.cpp:575-594):
         (dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k, blockmask,
@@ -348,13 +349,16 @@ def bwd_block(*args):
         (dout, q, k, v, out, lse, dq, dk, dv, cu_q, cu_k, blockmask, max_q, max_k, p_dropout, scale,
          causal, gen) = args
         return bwd(dout, q, k, v, out, lse, dq, dk, dv, cu_q, cu_k, max_q, max_k, p_dropout, scale,
-                   False, causal, gen, _blockmask=blockmask)
+                   False, causal, gen, _blockmask=blockmask, philox=philox)
     if len(args) == 12:
         (dout, qkv, out, _s_dmask, lse, cu, blockmask, p_dropout, scale, max_s, causal, gen) = args
         _require(qkv.dim() == 4 and qkv.shape[1] == 3, "qkv must be (total, 3, heads, head_dim)")
         dqkv = torch.empty_like(qkv)
         res = bwd(dout.contiguous(), qkv[:, 0], qkv[:, 1], qkv[:, 2], out, lse, dqkv[:, 0],
                   dqkv[:, 1], dqkv[:, 2], cu, cu, max_s, max_s, p_dropout, scale, False, causal, gen,
-                  _blockmask=blockmask)
+                  _blockmask=blockmask, philox=philox)
         return dqkv, None, res[3]
     raise TypeError("bwd_block takes 12 or 18 positional arguments, got %d" % len(args))
+
+
+bwd_block.accepted_arities = (12, 18)

@@ -10,8 +10,8 @@ from .flash_blocksparse_attn_interface import convert_blockmask, flash_blockspar
 
 def _make_layout(sparsity_config, max_seq_length):
     """`sparsity_config` may be a ready 0/1 layout tensor of shape (seq/16, seq/256), an object with
-    a make_layout(seq_len) method, or a hydra config describing such an object (the reference's
-    only form, :27-33; hydra is imported only in that case)."""
+    a make_layout(seq_len) method (sparsity_layouts.py has several), or a hydra config describing
+    such an object (the reference's only form, :27-33; hydra is imported only in that case)."""
     if torch.is_tensor(sparsity_config):
         return sparsity_config
     if not hasattr(sparsity_config, "make_layout"):
@@ -39,6 +39,7 @@ class FlashBlocksparseAttention(nn.Module):
             layout = layout.to(device)
         self.register_buffer("layout", layout)
         self.register_buffer("blockmask_converted", convert_blockmask(self.layout, causal=False))
+        self.register_buffer("blockmask_converted_causal", convert_blockmask(self.layout, causal=True))
 
     def _layout_for(self, seqlen):
         rounded = ((seqlen + 255) // 256) * 256
@@ -61,7 +62,8 @@ class FlashBlocksparseAttention(nn.Module):
                 out = flash_blocksparse_attn_func(qkv, cu_seqlens, self._layout_for(max_s), p, max_s,
                                                   softmax_scale=self.softmax_temp, causal=causal)
             else:
-                out = flash_blocksparse_attn_func(qkv, cu_seqlens, self.blockmask_converted, p, max_s,
+                converted = self.blockmask_converted_causal if causal else self.blockmask_converted
+                out = flash_blocksparse_attn_func(qkv, cu_seqlens, converted, p, max_s,
                                                   softmax_scale=self.softmax_temp, causal=causal,
                                                   convert_mask=False)
             return out, None

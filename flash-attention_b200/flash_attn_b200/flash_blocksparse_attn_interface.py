@@ -12,12 +12,23 @@ from . import flash_attn_cuda
 def convert_blockmask(blockmask, causal):
     """0/1 layout (rows, cols) -> int32 (cols, rows): row c lists, in ascending order, 4 * r for
     every non-zero (r, c), plus 1 when c is the first non-zero column of row r and plus 2 when it
-    is the last; the rest of the row is -1.  Same output as the reference function (:8-40)."""
-    assert not causal
+    is the last; the rest of the row is -1.  Same output as the reference function (:8-40).
+
+    causal=True (the reference asserts `not causal`, :21): blocks that lie entirely above the
+    diagonal -- first key column 256 * c behind the last query row 16 * r + 15 -- are removed
+    from the layout first, so they are neither visited nor counted; inside the remaining blocks
+    the kernels apply the causal mask element by element.  The dropout mask of a causal call is
+    the block-sparse one of the reduced layout: as in the reference's block kernels, the Philox
+    iteration index follows the visit lists alone (csrc/flash_attn/src/
+    fmha_block_fprop_kernel_1xN.h:205-232 takes its loop bounds from the block mask, with no
+    causal start row)."""
     mask = blockmask != 0
     nrow, ncol = mask.shape
     device = mask.device
     cols = torch.arange(ncol, device=device)
+    if causal:
+        last_query = 16 * torch.arange(nrow, device=device)[:, None] + 15
+        mask = mask & (256 * cols[None, :] <= last_query)
     # first / last non-zero column of each row (ncol / -1 when the row is empty)
     first = torch.where(mask, cols[None, :], torch.full_like(cols, ncol)[None, :]).min(dim=1).values
     last = torch.where(mask, cols[None, :], torch.full_like(cols, -1)[None, :]).max(dim=1).values

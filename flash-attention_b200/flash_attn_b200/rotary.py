@@ -116,3 +116,27 @@ class RotaryEmbedding2D(torch.nn.Module):
         if seq_dimension == -3:
             qe, ke = qe.transpose(1, 2), ke.transpose(1, 2)
         return qe, ke
+
+    def apply_qkv(self, qkv):
+        """(batch, seqlen, 3, heads, d) with seqlen = side * side -> q and k rotated, v unchanged,
+        in one pass of the same kernel the 1-D embedding uses: the 2-D scheme is a per-position
+        angle table like any other -- token p = row * side + col turns the channel pairs of the
+        first half of d by col * f_i and those of the second half by row * f_i, f_i the
+        frequencies of a (d / 2)-wide 1-D embedding (reference flash_attn/rotary.py:103-135)."""
+        if not RotaryEmbedding.fused_path(qkv):
+            q, k, v = qkv.unbind(dim=2)
+            q, k = self.forward(q, k, seq_dimension=-3)
+            return torch.stack([q, k, v], dim=2)
+        seqlen = qkv.shape[1]
+        side = int(math.sqrt(seqlen))
+        assert side * side == seqlen
+        key = (seqlen, qkv.device)
+        if getattr(self, "_table_key", None) != key:
+            inv_freq = self.rotary_emb1d.inv_freq.to(qkv.device)          # d / 4 frequencies
+            pos = torch.arange(seqlen, device=qkv.device)
+            col = (pos % side).to(inv_freq.dtype)
+            row = torch.div(pos, side, rounding_mode="floor").to(inv_freq.dtype)
+            ang = torch.cat([torch.outer(col, inv_freq), torch.outer(row, inv_freq)], dim=-1)   # (seqlen, d / 2)
+            self._cos_table, self._sin_table = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+            self._table_key = key
+        return _RotaryQKV.apply(qkv, self._cos_table, self._sin_table)

@@ -1,8 +1,8 @@
 """Generates the golden fixtures in this directory from the reference's own Python code.
 
-Run once in a container that has the reference tree (default /root/reference):
+Run once where a checkout of the reference (lw921014/flash-attention) is available:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference      (or FA_REFERENCE_ROOT=... in the environment)
 
 * attention_ref      is cut out of benchmarks/benchmark_flash_attention.py with `ast` (the script
                      itself cannot be imported: it imports the CUDA extension and runs GPU code at
@@ -22,7 +22,7 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = None  # root of the reference checkout; set by the command line below
 
 
 def extract_function(path, name, extra_globals):
@@ -123,4 +123,7 @@ def main():
 
 
 if __name__ == "__main__":
+    REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FA_REFERENCE_ROOT")
+    if not REF or not os.path.isdir(os.path.join(REF, "flash_attn")):
+        sys.exit("usage: make_golden.py /path/to/reference (a checkout of lw921014/flash-attention)")
     main()

@@ -151,3 +151,68 @@ def test_blocksparse_module_paths():
     mha = FlashBlocksparseMHA(128, 2, layout, max_seq_length=512, device="cuda", dtype=torch.float16)
     y, _ = mha(torch.randn(2, 512, 128, device="cuda", dtype=torch.float16))
     assert y.shape == (2, 512, 128) and not torch.isnan(y).any()
+
+
+@pytest.mark.parametrize("p,lens", [(0.0, [1024, 700]), (0.15, [768, 300])])
+def test_causal_blocksparse_parity(p, lens):
+    """Causal + layout (not available in the reference, which asserts `not causal`): the result is
+    standard attention under (layout AND key <= query), with the dropout mask of the block-sparse
+    walk over the layout that convert_blockmask(causal=True) leaves."""
+    from flash_attn_b200.flash_blocksparse_attn_interface import convert_blockmask
+    from flash_attn_b200.sparsity_layouts import RandomLayout
+    from flash_attn_b200 import flash_attn_cuda as fc
+    S, heads = 1024, 2
+    layout = RandomLayout(0.4, seed=7).make_layout(S).cuda()
+    conv = convert_blockmask(layout, True)
+    q, k, v, dout, cu, _ = U.make_varlen(lens, lens, heads, 64, torch.float16, seed=23)
+    torch.cuda.manual_seed(3)
+    out, lse, seed, offset = fc.fwd_block(q, k, v, cu, cu, conv, S, S, p, 0.125, True, False, None,
+                                          return_philox=True)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    fc.bwd_block(dout, q, k, v, out, lse, dq, dk, dv, cu, cu, conv, S, S, p, 0.125, True, None,
+                 philox=(seed, offset))
+    torch.cuda.synchronize()
+    fc.check_device_status()
+    conv_np = conv.cpu().numpy()
+    allowed, keep = [], []
+    for b, n in enumerate(lens):
+        a = orc.blocksparse_allowed(conv_np, n, n)
+        allowed.append(torch.from_numpy(a))
+        if p > 0:
+            it = orc.blocksparse_walk(conv_np, n, n)
+            keep.append(torch.from_numpy(np.stack([
+                orc.dropout_keep_mask(seed, offset, b, h, heads, n, n, p, 256, False, bs_iter=it)
+                for h in range(heads)])))
+    kw = dict(dropout_p=p, keep_masks=keep if p > 0 else None, allowed=allowed)
+    o32, dq32, dk32, dv32 = U.oracle_cpu(q, k, v, dout, cu, cu, 0.125, True, **kw)
+    o16, dq16, dk16, dv16 = U.oracle_cpu(q, k, v, dout, cu, cu, 0.125, True, dtype=torch.float16, **kw)
+    U.assert_within_2x("out", out, o32, o16)
+    U.assert_within_2x("dq", dq, dq32, dq16)
+    U.assert_within_2x("dk", dk, dk32, dk16)
+    U.assert_within_2x("dv", dv, dv32, dv16)
+    # a mask converted without the causal pruning gives the same numbers when dropout is off
+    if p == 0.0:
+        conv_full = convert_blockmask(layout, False)
+        out2, lse2 = fc.fwd_block(q, k, v, cu, cu, conv_full, S, S, 0.0, 0.125, True, False, None)
+        torch.cuda.synchronize()
+        assert torch.equal(out2, out)
+        for b, n in enumerate(lens):
+            assert torch.equal(lse2[b, :, :n], lse[b, :, :n])
+
+
+def test_blocksparse_module_with_a_layout_generator_and_causal():
+    from flash_attn_b200.flash_blocksparse_attention import FlashBlocksparseAttention
+    from flash_attn_b200.sparsity_layouts import DenseLayout, SlidingWindowLayout
+    from flash_attn_b200.flash_attention import FlashAttention
+    torch.manual_seed(0)
+    qkv = torch.randn(2, 512, 3, 2, 64, device="cuda", dtype=torch.float16)
+    dense = FlashAttention().cuda().eval()
+    sparse = FlashBlocksparseAttention(DenseLayout(), max_seq_length=512).cuda().eval()
+    for causal in (False, True):
+        a, _ = dense(qkv, causal=causal)
+        b, _ = sparse(qkv, causal=causal)
+        assert U.max_err(a, b) < 2e-3
+    win = FlashBlocksparseAttention(SlidingWindowLayout(0, 0), max_seq_length=512).cuda().eval()
+    c, _ = win(qkv)   # block-diagonal: the second 256 tokens do not see the first
+    d, _ = dense(qkv[:, 256:].contiguous())
+    assert U.max_err(c[:, 256:], d) < 2e-3

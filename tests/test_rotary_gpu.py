@@ -72,3 +72,39 @@ def test_flash_mha_uses_the_fused_rotation():
     ctx, _ = mha.inner_attn(torch.stack([q, k, v], dim=2), causal=False)
     y2 = mha.out_proj(ctx.reshape(2, 64, 128))
     assert (y.float() - y2.float()).abs().max().item() < 5e-3
+
+
+@pytest.mark.parametrize("dtype,b,side,h,d", [(torch.float16, 2, 7, 3, 64), (torch.bfloat16, 1, 16, 2, 128),
+                                              (torch.float16, 2, 5, 1, 32)])
+def test_rotary_2d_qkv_matches_the_unfused_module(dtype, b, side, h, d):
+    """The 2-D embedding through the one-pass kernel (a per-position table of column / row angles)
+    against the module's framework-op path, which follows flash_attn/rotary.py:103-135."""
+    from flash_attn_b200.rotary import RotaryEmbedding2D
+    s = side * side
+    g = torch.Generator(device="cuda").manual_seed(side + d)
+    qkv = torch.randn(b, s, 3, h, d, device="cuda", generator=g).to(dtype)
+    rope = RotaryEmbedding2D(d).cuda()
+    got = rope.apply_qkv(qkv)
+    q, k = rope(qkv[:, :, 0].float(), qkv[:, :, 1].float(), seq_dimension=-3)
+    eps = 2.0 ** -8 if dtype is torch.bfloat16 else 2.0 ** -11
+    scale = max(q.abs().max().item(), k.abs().max().item())
+    assert (got[:, :, 0].float() - q).abs().max().item() <= eps * scale + 1e-6
+    assert (got[:, :, 1].float() - k).abs().max().item() <= eps * scale + 1e-6
+    assert torch.equal(got[:, :, 2], qkv[:, :, 2])
+    # token 0 (row 0, column 0) is not rotated at all; token 1 (column 1) only in its first half
+    assert torch.equal(got[:, 0, :2], qkv[:, 0, :2])
+    assert torch.equal(got[:, 1, :2, :, d // 2:], qkv[:, 1, :2, :, d // 2:])
+
+
+def test_flash_mha_2d_rotary_runs_fused():
+    from flash_attn_b200.flash_attention import FlashMHA
+    torch.manual_seed(0)
+    mha = FlashMHA(128, 2, use_rotary_emb="2d", device="cuda", dtype=torch.float16)
+    x = torch.randn(2, 49, 128, device="cuda", dtype=torch.float16)
+    y, _ = mha(x)
+    qkv = mha.Wqkv(x).reshape(2, 49, 3, 2, 64)
+    q, k, v = qkv.unbind(dim=2)
+    q, k = mha.rotary_emb(q, k, seq_dimension=-3)
+    ctx, _ = mha.inner_attn(torch.stack([q, k, v], dim=2), causal=False)
+    y2 = mha.out_proj(ctx.reshape(2, 49, 128))
+    assert (y.float() - y2.float()).abs().max().item() < 5e-3
