@@ -5,8 +5,10 @@
 Workload (default): BERT-base-shaped varlen training attention -- batch 8, 12 heads, head_dim 64,
 fp16, max_seqlen 4096, per-sequence lengths uniform in [max/2, max] from a seed, packed with
 cu_seqlens, dropout 0.1, non-causal, Q/K/V/dO ~ N(0,1); synthetic data standing in for the
-BERT-base attention shapes of the reference's speed-up chart.  One step = one forward + backward
-pass over that batch.  Metric: algorithmic TFLOP/s, 3.5 * 4 * d * heads * sum(s_i^2) per step.
+BERT-base attention shapes of the reference's speed-up chart.  One step = `passes_per_step`
+forward + backward passes over that batch (so many that the timed region of K steps lasts about a
+second and the clock samples fall inside it).  Metric: algorithmic TFLOP/s,
+3.5 * 4 * d * heads * sum(s_i^2) per pass.
 
 The printed JSON line follows the driver's contract: `value` is measured with inputs resident in
 HBM, `e2e` through the public functional API with pinned host buffers copied in and results
@@ -14,7 +16,10 @@ copied out inside the timed region, `roofline` for the dominant kernel (backward
 against the measured tensor-core peak, `cpu_baseline` = the CPU oracle (standard attention in
 fp32) timed on a bounded sample on this host.  With N > 1 (one process per GPU under torchrun)
 every rank runs its own batch shard (weak scaling, no data-path collective) and the outputs are
-re-assembled with one NCCL all-gather per step.
+re-assembled with one NCCL all-gather per pass, on a side stream with few CTAs so that it does not
+displace the attention kernels; `ms_per_step_no_gather` is the same loop without it.  The line also
+carries `long_context` (batch 2 x 32 heads x 65536, causal, bf16: this rank's 32 / N heads, forward +
+backward, with and without the all-gather of the outputs over NVLink) and `causal_lm_d128_S4096`.
 """
 import argparse
 import json
@@ -35,6 +40,7 @@ import torch  # noqa: E402
 
 BATCH, HEADS, HEAD_DIM = 8, 12, 64
 DROPOUT_P = 0.1
+CPU_SAMPLE_HEADS = 4  # heads of the bounded sample the CPU legs run (a pass over all 12 takes ~10 s)
 METRIC = "fwd+bwd attention TFLOP/s (algorithmic, 3.5 x forward)"
 
 
@@ -111,22 +117,26 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_attention_sample(seqlen, heads, d, causal, threads, repeats=1, min_seconds=0.0):
-    """fwd+bwd of the oracle's standard attention (fp32) for one sequence of `seqlen` tokens, run
-    `repeats` times after a warm-up pass and then until `min_seconds` of timed work have been done;
-    returns (mean seconds per pass, flops per pass, passes timed)."""
+def cpu_attention_sample(seqlens, heads, d, causal, dropout_p, threads, repeats=1, min_seconds=0.0):
+    """fwd+bwd of the reference's standard attention (the oracle's restatement of `attention_ref`,
+    fp32, dropout through the framework's own dropout as the reference does) over the sequences
+    `seqlens`, one at a time; run `repeats` times after a warm-up pass and then until `min_seconds`
+    of timed work have been done; returns (mean seconds per pass over all of them, flops per pass,
+    passes timed)."""
     from oracle import attention_oracle as orc
     torch.set_num_threads(threads)
     g = torch.Generator().manual_seed(0)
-    qkv = torch.randn(1, seqlen, 3, heads, d, generator=g, requires_grad=True)
-    dout = torch.randn(1, seqlen, heads, d, generator=g)
-    mask = torch.ones(1, seqlen, dtype=torch.bool)
+    data = []
+    for n in seqlens:
+        qkv = torch.randn(1, n, 3, heads, d, generator=g, requires_grad=True)
+        data.append((qkv, torch.randn(1, n, heads, d, generator=g), torch.ones(1, n, dtype=torch.bool)))
 
     def one_pass():
-        qkv.grad = None
         t0 = time.perf_counter()
-        out = orc.attention_ref(qkv, mask, 0.0, upcast=True, causal=causal)
-        out.backward(dout)
+        for qkv, dout, mask in data:
+            qkv.grad = None
+            out = orc.attention_ref(qkv, mask, dropout_p, upcast=True, causal=causal)
+            out.backward(dout)
         return time.perf_counter() - t0
 
     one_pass()  # warm-up
@@ -134,35 +144,44 @@ def cpu_attention_sample(seqlen, heads, d, causal, threads, repeats=1, min_secon
     while n < repeats or (total < min_seconds and n < 400):
         total += one_pass()
         n += 1
-    return total / n, 3.5 * fwd_flops([seqlen], heads, d, causal), n
+    return total / n, 3.5 * fwd_flops(seqlens, heads, d, causal), n
+
+
+def cpu_sample_lengths(lengths):
+    """The bounded sample of the workload the CPU legs run: its longest and its shortest sequence."""
+    return [max(lengths), min(lengths)]
 
 
 def run_reference(args):
     """--impl reference: the reference's CPU implementation of the path (its standard attention,
     restated in oracle/, since the reference tree is not present on the GPU box and its CUDA
-    kernels target sm75/sm80 only) on all host threads, on a bounded sample of the workload."""
+    kernels target sm75/sm80 only) on all host threads, on a bounded sample of the workload: the
+    longest and the shortest of its sequences, all heads, dropout on."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = os.cpu_count() or 1
     lengths = workload_lengths(args.seqlen, args.seed)
-    sample_len = min(max(lengths), 2048)
+    sample = cpu_sample_lengths(lengths)
     times = []
     flops = 0.0
     for i in range(args.warmup + args.steps):
-        dt, flops, _ = cpu_attention_sample(sample_len, HEADS, HEAD_DIM, False, threads, repeats=4)
+        dt, flops, _ = cpu_attention_sample(sample, CPU_SAMPLE_HEADS, HEAD_DIM, False, DROPOUT_P, threads, repeats=1)
         if i >= args.warmup:
             times.append(dt)
     t = float(np.mean(times))
     value = flops / t / 1e12
-    sample = ("each step: 4 passes over 1 sequence of %d tokens x %d heads, dropout off, fp32 standard "
-              "attention fwd+bwd" % (sample_len, HEADS))
+    desc = ("sample of the workload: each step = 1 pass over its longest and its shortest sequence (%d and %d "
+            "tokens) x %d of the %d heads, dropout %.1f, fp32 standard attention fwd+bwd"
+            % (sample[0], sample[1], CPU_SAMPLE_HEADS, HEADS, DROPOUT_P))
+    cfg = workload_config(args, lengths)
+    cfg["workload"] = cfg["workload"] + " -- CPU arm runs a SAMPLE of it (see cpu_baseline.sample)"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args, lengths),
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "config": cfg,
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -187,6 +206,10 @@ def main():
     ap.add_argument("--seqlen", type=int, default=4096)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--no-long-context", action="store_true",
+                    help="skip the head-sharded 65536-token block (for quick runs)")
+    ap.add_argument("--passes", type=int, default=0,
+                    help="forward+backward passes per step (0 = as many as make K steps last about 1 s)")
     ap.add_argument("--only-extra", default=None, metavar="NAME",
                     help="run just one entry of the extras sweep (e.g. causal_lm_bf16_d128_S4096) and "
                          "print it; for profiler captures of the other configurations")
@@ -211,6 +234,9 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # The only collective is the re-assembly of outputs, which runs beside attention kernels that
+        # want every SM: keep NCCL's kernels to a few CTAs.
+        os.environ.setdefault("NCCL_MAX_CTAS", "4")
         dist.init_process_group("nccl", device_id=dev)
 
     if args.only_extra:
@@ -235,25 +261,33 @@ def main():
     torch.cuda.manual_seed(1234)
     side = torch.cuda.Stream(device=dev)
 
-    def step_resident():
+    gathered = torch.empty((world * total, HEADS, HEAD_DIM), dtype=torch.float16, device=dev) if world > 1 else None
+
+    def one_pass(gather):
         """forward + backward through the extension-module contract (C ABI), data in HBM."""
-        state = gen.get_state()
-        out, lse = fc.fwd(q, k, v, cu, cu, max_s, max_s, DROPOUT_P, scale, False, False, False, None)
-        finish = None
-        if world > 1:
+        out, lse, seed, offset = fc.fwd(q, k, v, cu, cu, max_s, max_s, DROPOUT_P, scale, False, False, False,
+                                        None, return_philox=True)
+        if gather:
+            # re-assembly of the outputs of all ranks, ordered by streams only (no host wait)
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                gathered, work = parallel.all_gather_tokens(out, async_op=True)
-            finish = (gathered, work)
-        after = gen.get_state()
-        gen.set_state(state)  # the backward regenerates the forward's mask
+                out.record_stream(side)
+                dist.all_gather_into_tensor(gathered, out)
         fc.bwd(dout, q, k, v, out, lse, dqkv[:, 0], dqkv[:, 1], dqkv[:, 2], cu, cu, max_s, max_s,
-               DROPOUT_P, scale, False, False, None)
-        gen.set_state(after)
-        if finish is not None:
-            finish[1].wait()
+               DROPOUT_P, scale, False, False, None, philox=(seed, offset))
+        if gather:
             torch.cuda.current_stream().wait_stream(side)
         return out
+
+    state = {"passes": 1}
+
+    def step_resident():
+        for _ in range(state["passes"]):
+            one_pass(world > 1)
+
+    def step_no_gather():
+        for _ in range(state["passes"]):
+            one_pass(False)
 
     def timed(fn, steps, warmup):
         for _ in range(warmup):
@@ -285,9 +319,21 @@ def main():
     sampler = ClockSampler(local_rank)
     sampler.start()
     time.sleep(0.3)  # let the first samples arrive before the timed region starts
+    # passes per step: enough that the K timed steps last about a second
+    if args.passes > 0:
+        state["passes"] = args.passes
+    else:
+        est = timed(step_resident, 3, 2)
+        if world > 1:
+            t = torch.tensor([est], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            est = t.item()
+        state["passes"] = max(1, min(200, int(math.ceil(1000.0 / (args.steps * est)))))
+    passes = state["passes"]
     ms_step = timed(step_resident, args.steps, args.warmup)
     fc.check_device_status(dev)
-    value = world * flops_step / (ms_step * 1e-3) / 1e12
+    value = world * passes * flops_step / (ms_step * 1e-3) / 1e12
+    ms_step_no_gather = timed(step_no_gather, args.steps, 1) if world > 1 else None
 
     # ------------------------------------------------------------------ end to end (host buffers)
     # Every step copies its inputs from pinned host memory, runs forward + backward through the
@@ -359,6 +405,7 @@ def main():
             ms = tt.item()
         return ms
 
+    state["passes"] = 1
     ms_e2e = timed_e2e(max(4, args.steps), 4) if not args.kernels_only else float("nan")
     e2e_value = world * flops_step / (ms_e2e * 1e-3) / 1e12
     h2d = qkv_host[0].numel() * 2 + dout_host[0].numel() * 2
@@ -397,26 +444,36 @@ def main():
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
-        "config": workload_config(args, lengths),
+        "config": dict(workload_config(args, lengths), passes_per_step=passes),
+        "ms_per_pass": ms_step / passes,
+        "ms_per_step_no_gather": ms_step_no_gather,
         "pct_of_peak": 100.0 * value / world / peaks["tflops"],
         "fwd_tflops_per_gpu": flops_fwd / (ms_fwd * 1e-3) / 1e12,
         "bwd_tflops_per_gpu": 2.5 * flops_fwd / (ms_bwd * 1e-3) / 1e12,
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": 4 * args.steps,
+        "gpu_launches": 4 * passes * args.steps,
         "roofline": roofline,
     }
 
+    # free the headline buffers before the other blocks
+    del qkv_host, dout_host, out_host, dqkv_host, qkv_dev, dout_dev
+    if world == 1 and not args.kernels_only:
+        line["causal_lm_d128_S4096"] = causal_lm_block(fc, dev, peaks, 4096, iters=20)
+    if not args.kernels_only and not args.no_long_context and HEADS_LONG % world == 0:
+        line["long_context"] = long_context_block(fc, parallel, dist, dev, world, rank, peaks,
+                                                  iters=20 if world > 1 else 10)
     if rank == 0 and world == 1 and not args.kernels_only:
         threads = os.cpu_count() or 1
-        sample_len = min(max(lengths), 2048)
-        dt, fl, passes = cpu_attention_sample(sample_len, HEADS, HEAD_DIM, False, threads, repeats=2,
-                                              min_seconds=10.0)
+        sample = cpu_sample_lengths(lengths)
+        dt, fl, n_cpu = cpu_attention_sample(sample, CPU_SAMPLE_HEADS, HEAD_DIM, False, DROPOUT_P, threads,
+                                             repeats=1, min_seconds=10.0)
         line["cpu_baseline"] = {
             "value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-            "sample": "%d passes (about 10 s) over 1 sequence of %d tokens x %d heads, fp32 standard "
-                      "attention fwd+bwd, dropout off" % (passes, sample_len, HEADS)}
+            "sample": "%d passes (about 10 s) over the longest and the shortest sequence of the workload (%d and "
+                      "%d tokens) x %d of the %d heads, fp32 standard attention fwd+bwd, dropout %.1f"
+                      % (n_cpu, sample[0], sample[1], CPU_SAMPLE_HEADS, HEADS, DROPOUT_P)}
         if not args.no_extras:
             line["extras"] = extras(fc, dev, peaks)
     if rank == 0:
@@ -425,8 +482,112 @@ def main():
         dist.destroy_process_group()
 
 
+HEADS_LONG = 32
+
+
+def _time_passes(fn, iters, warmup=2):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def long_context_block(fc, parallel, dist, dev, world, rank, peaks, iters):
+    """Long-context attention sharded by head: batch 2 x 32 heads x 65536 tokens x d 64, causal, bf16,
+    dropout 0.  Rank r holds heads [r * 32 / N, (r + 1) * 32 / N); the data of a head does not
+    depend on N (seeded per head).  Times this rank's forward + backward with and without the
+    all-gather of the output shards over NVLink (one collective per pass on a side stream, ordered
+    by streams); the slowest rank's time is reported.  FLOPs count half of the full problem
+    (4 d H B S^2 / 2)."""
+    B, H, d, S = 2, HEADS_LONG, 64, 65536
+    hs = H // world
+    h0 = rank * hs
+
+    def head_stack(tag):
+        cols = []
+        for h in range(h0, h0 + hs):
+            gh = torch.Generator(device=dev).manual_seed(9000 + 10 * h + tag)
+            cols.append(torch.randn(B * S, d, device=dev, dtype=torch.bfloat16, generator=gh))
+        return torch.stack(cols, dim=1).contiguous()
+
+    q, k, v, dout = head_stack(0), head_stack(1), head_stack(2), head_stack(3)
+    cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=dev)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    side = torch.cuda.Stream(device=dev)
+    keep = {}
+
+    def one_pass(gather):
+        out, lse = fc.fwd(q, k, v, cu, cu, S, S, 0.0, 0.125, False, True, False, None)
+        if gather:
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                out.record_stream(side)
+                keep["full"] = parallel.all_gather_heads(out)      # (B * S, 32, d) on every rank
+        fc.bwd(dout, q, k, v, out, lse, dq, dk, dv, cu, cu, S, S, 0.0, 0.125, False, True, None)
+        if gather:
+            torch.cuda.current_stream().wait_stream(side)
+
+    def fwd_only():
+        fc.fwd(q, k, v, cu, cu, S, S, 0.0, 0.125, False, True, False, None)
+
+    def slowest(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev)
+        dist.barrier()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    if world > 1:
+        dist.barrier()
+    ms_fwd = slowest(_time_passes(fwd_only, iters, warmup=1))
+    ms_plain = slowest(_time_passes(lambda: one_pass(False), iters, warmup=1))
+    ms_gather = slowest(_time_passes(lambda: one_pass(True), iters, warmup=1)) if world > 1 else None
+    fc.check_device_status(dev)
+    fl = fwd_flops([S] * B, hs, d, causal=True)
+    res = {"workload": "batch 2 x 32 heads x 65536 tokens x d 64, causal, bf16, dropout 0; %d heads per GPU" % hs,
+           "heads_per_gpu": hs, "iters": iters, "fwd_ms": ms_fwd, "fwd_bwd_ms": ms_plain,
+           "fwd_tflops_per_gpu": fl / ms_fwd / 1e9, "fwd_pct_peak": 100 * fl / ms_fwd / 1e9 / peaks["tflops"],
+           "fwd_bwd_tflops_per_gpu": 3.5 * fl / ms_plain / 1e9,
+           "fwd_bwd_pct_peak": 100 * 3.5 * fl / ms_plain / 1e9 / peaks["tflops"],
+           "fwd_bwd_tflops_all_gpus": world * 3.5 * fl / ms_plain / 1e9}
+    if ms_gather is not None:
+        res["fwd_bwd_ms_with_gather"] = ms_gather
+        res["fwd_bwd_tflops_per_gpu_with_gather"] = 3.5 * fl / ms_gather / 1e9
+        res["gathered_bytes_per_gpu"] = int(B * S * H * d * 2)
+    del q, k, v, dout, dq, dk, dv
+    keep.clear()
+    return res
+
+
+def causal_lm_block(fc, dev, peaks, S, iters):
+    """Causal LM attention, bf16: batch 16 x 12 heads x d 128 x S tokens, dropout 0 (FLOPs: half of the
+    full problem)."""
+    B, H, d = 16, 12, 128
+    g = torch.Generator(device=dev).manual_seed(11)
+    mk = lambda: torch.randn(B * S, H, d, device=dev, dtype=torch.bfloat16, generator=g)
+    q, k, v, dout = mk(), mk(), mk(), mk()
+    cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=dev)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    sc = d ** -0.5
+    out, lse = fc.fwd(q, k, v, cu, cu, S, S, 0.0, sc, False, True, False, None)
+    f = _time_passes(lambda: fc.fwd(q, k, v, cu, cu, S, S, 0.0, sc, False, True, False, None), iters)
+    b = _time_passes(lambda: fc.bwd(dout, q, k, v, out, lse, dq, dk, dv, cu, cu, S, S, 0.0, sc, False, True, None),
+                     iters)
+    fl = fwd_flops([S] * B, H, d, causal=True)
+    return {"iters": iters, "fwd_ms": f, "bwd_ms": b, "fwd_tflops": fl / f / 1e9,
+            "fwd_pct_peak": 100 * fl / f / 1e9 / peaks["tflops"], "fwd_bwd_tflops": 3.5 * fl / (f + b) / 1e9,
+            "fwd_bwd_pct_peak": 100 * 3.5 * fl / (f + b) / 1e9 / peaks["tflops"]}
+
+
 def extras(fc, dev, peaks, only=None):
-    """Short sweeps over the other benchmark configurations (few iterations each, kernel time
+    """Sweeps over the other benchmark configurations (20 iterations each after warm-up, kernel time
     only, data resident): reported for context, not part of the headline value.  `only` limits
     the sweep to one named entry."""
     res = {}
@@ -434,7 +595,7 @@ def extras(fc, dev, peaks, only=None):
     def wanted(name):
         return only is None or only == name
 
-    def time_fwd_bwd(q, k, v, dout, cu, S, p, causal, scale, iters=5):
+    def time_fwd_bwd(q, k, v, dout, cu, S, p, causal, scale, iters=20):
         out, lse = fc.fwd(q, k, v, cu, cu, S, S, p, scale, False, causal, False, None)
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
@@ -529,7 +690,7 @@ def extras(fc, dev, peaks, only=None):
         k = torch.randn(B * S, H, d, device=dev, dtype=torch.bfloat16, generator=g)
         v = torch.randn(B * S, H, d, device=dev, dtype=torch.bfloat16, generator=g)
         dout = torch.randn(B * S, H, d, device=dev, dtype=torch.bfloat16, generator=g)
-        f, b = time_fwd_bwd(q, k, v, dout, cu, S, 0.0, True, d ** -0.5, iters=3)
+        f, b = time_fwd_bwd(q, k, v, dout, cu, S, 0.0, True, d ** -0.5)
         fl = fwd_flops([S] * B, H, d, causal=True)
         res["causal_lm_bf16_d128_S%d" % S] = {
             "fwd_ms": f, "bwd_ms": b, "fwd_tflops": fl / f / 1e9, "fwd_bwd_tflops": 3.5 * fl / (f + b) / 1e9,
@@ -557,16 +718,16 @@ def extras(fc, dev, peaks, only=None):
             if it == 1:
                 torch.cuda.synchronize()
                 ev[0].record()
-            for _ in range(3):
+            for _ in range(20):
                 fc.fwd_block(q, k, v, cu, cu, conv, S, S, DROPOUT_P, 0.125, False, False, None)
             if it == 1:
                 ev[1].record()
-            for _ in range(3):
+            for _ in range(20):
                 fc.bwd_block(dout, q, k, v, out, lse, dq, dk, dv, cu, cu, conv, S, S, DROPOUT_P, 0.125,
                              False, None)
         ev[2].record()
         torch.cuda.synchronize()
-        f, b = ev[0].elapsed_time(ev[1]) / 3, ev[1].elapsed_time(ev[2]) / 3
+        f, b = ev[0].elapsed_time(ev[1]) / 20, ev[1].elapsed_time(ev[2]) / 20
         density = float(blocks.float().mean())
         fl = 4.0 * d * H * B * float(S) * float(S) * density   # work of the blocks in the layout
         res["blocksparse_fp16_d64_S4096"] = {
@@ -588,25 +749,25 @@ def extras(fc, dev, peaks, only=None):
             if it == 1:
                 torch.cuda.synchronize()
                 ev[0].record()
-            for _ in range(5):
+            for _ in range(20):
                 bp.gather_rows(x, idx)
             if it == 1:
                 ev[1].record()
-            for _ in range(5):
+            for _ in range(20):
                 bp.scatter_rows(packed, idx, B * S)
             if it == 1:
                 ev[2].record()
-            for _ in range(5):
+            for _ in range(20):
                 x.index_select(0, idx)
             if it == 1:
                 ev[3].record()
-            for _ in range(5):
+            for _ in range(20):
                 x.new_zeros((B * S, D)).index_copy_(0, idx, packed)
         ev[4].record()
         torch.cuda.synchronize()
         row = D * 2
         n = idx.numel()
-        t = [ev[i].elapsed_time(ev[i + 1]) / 5 for i in range(4)]
+        t = [ev[i].elapsed_time(ev[i + 1]) / 20 for i in range(4)]
         gather_bytes = 2 * n * row + 8 * n                 # rows read + written, indices
         scatter_bytes = n * row + B * S * row + 8 * n + 8 * B * S   # rows read, output written once, index maps
         res["unpad_pad_fp16_B64_S512_D2304"] = {
@@ -627,16 +788,16 @@ def extras(fc, dev, peaks, only=None):
             if it == 1:
                 torch.cuda.synchronize()
                 ev[0].record()
-            for _ in range(5):
+            for _ in range(20):
                 rope.apply_qkv(qkv)
             if it == 1:
                 ev[1].record()
-            for _ in range(5):
+            for _ in range(20):
                 q_, k_ = rope(qkv[:, :, 0], qkv[:, :, 1], seq_dimension=-3)
                 torch.stack([q_, k_, qkv[:, :, 2]], dim=2)
         ev[2].record()
         torch.cuda.synchronize()
-        t_fused, t_ops = ev[0].elapsed_time(ev[1]) / 5, ev[1].elapsed_time(ev[2]) / 5
+        t_fused, t_ops = ev[0].elapsed_time(ev[1]) / 20, ev[1].elapsed_time(ev[2]) / 20
         nbytes = 2 * qkv.numel() * 2
         res["rotary_qkv_fp16_B64_S512_H12_D64"] = {
             "fused_ms": t_fused, "fused_gbs": nbytes / t_fused / 1e6,
@@ -650,12 +811,39 @@ def extras(fc, dev, peaks, only=None):
         k = torch.randn(B * S, H, d, device=dev, dtype=torch.bfloat16, generator=g)
         v = torch.randn(B * S, H, d, device=dev, dtype=torch.bfloat16, generator=g)
         dout = torch.randn(B * S, H, d, device=dev, dtype=torch.bfloat16, generator=g)
-        f, b = time_fwd_bwd(q, k, v, dout, cu, S, 0.0, True, 0.125, iters=2)
+        f, b = time_fwd_bwd(q, k, v, dout, cu, S, 0.0, True, 0.125, iters=10)
         fl = fwd_flops([S] * B, H, d, causal=True)
         res["long_context_bf16_d64_S65536_4heads"] = {
             "fwd_ms": f, "bwd_ms": b, "fwd_tflops": fl / f / 1e9, "fwd_bwd_tflops": 3.5 * fl / (f + b) / 1e9,
             "fwd_pct_peak": 100 * fl / f / 1e9 / peaks["tflops"],
             "fwd_bwd_pct_peak": 100 * 3.5 * fl / (f + b) / 1e9 / peaks["tflops"]}
+        del q, k, v, dout
+    # dense attention without dropout / without the causal mask, and the cost of the deterministic dQ mode
+    dense = {"dense_fp16_d64_nodropout_S4096": (8, 12, 64, 4096, torch.float16, False, 0.0),
+             "dense_bf16_d128_noncausal_S4096": (16, 12, 128, 4096, torch.bfloat16, False, 0.0),
+             "dense_bf16_d64_causal_S16384": (2, 16, 64, 16384, torch.bfloat16, True, 0.0),
+             "dense_fp16_d64_dropout_S4096": (8, 12, 64, 4096, torch.float16, False, DROPOUT_P)}
+    for name, (B, H, d, S, dt, causal, p) in dense.items():
+        if not wanted(name):
+            continue
+        cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=dev)
+        q = torch.randn(B * S, H, d, device=dev, dtype=dt, generator=g)
+        k = torch.randn(B * S, H, d, device=dev, dtype=dt, generator=g)
+        v = torch.randn(B * S, H, d, device=dev, dtype=dt, generator=g)
+        dout = torch.randn(B * S, H, d, device=dev, dtype=dt, generator=g)
+        f, b = time_fwd_bwd(q, k, v, dout, cu, S, p, causal, d ** -0.5)
+        fc.options.deterministic = True
+        try:
+            _, b_det = time_fwd_bwd(q, k, v, dout, cu, S, p, causal, d ** -0.5)
+        finally:
+            fc.options.deterministic = False
+        fl = fwd_flops([S] * B, H, d, causal=causal)
+        res[name] = {"fwd_ms": f, "bwd_ms": b, "fwd_tflops": fl / f / 1e9, "bwd_tflops": 2.5 * fl / b / 1e9,
+                     "fwd_pct_peak": 100 * fl / f / 1e9 / peaks["tflops"],
+                     "bwd_pct_peak": 100 * 2.5 * fl / b / 1e9 / peaks["tflops"],
+                     "fwd_bwd_tflops": 3.5 * fl / (f + b) / 1e9,
+                     "fwd_bwd_pct_peak": 100 * 3.5 * fl / (f + b) / 1e9 / peaks["tflops"],
+                     "bwd_deterministic_ms": b_det, "deterministic_bwd_slowdown": b_det / b}
         del q, k, v, dout
     return res
 

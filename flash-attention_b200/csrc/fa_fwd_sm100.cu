@@ -375,6 +375,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       thr_term = fa_keep_thr_term(a.drop.threshold);
     }
 
+#ifdef FA_FWD_OFFSET
+    // experiment: start query tile 1 half a tile period behind query tile 0
+    if (g == 1) {
+      const long long t_start = clock64();
+      while (clock64() - t_start < FA_FWD_OFFSET) {}
+    }
+#endif
     FA_PROF_DECL
     for (int j = 0; j < n && ok; ++j) {
       const int col0 = kv_tile(j) * kBlockN;
