@@ -64,10 +64,15 @@ struct FwdShared {
 #define FA_PROF(slot) { const long long now_ = clock64(); prof_acc[slot] += now_ - prof_t; prof_t = now_; }
 #define FA_PROF_FLUSH(base, n) if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && a.status) { \
     for (int i_ = 0; i_ < 8; ++i_) a.status[(base) + i_] = static_cast<int32_t>(prof_acc[i_] / ((n) > 0 ? (n) : 1)); }
+// time stamps (low 32 bits of the SM clock) of the events of kv steps 5, 6 of CTA (0,0,0): slot =
+// 64 + (step - 5) * 24 + idx, for a timeline across the roles
+#define FA_STAMP(step, idx) if ((step) >= 5 && (step) <= 6 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && a.status) { \
+    a.status[64 + ((step) - 5) * 24 + (idx)] = static_cast<int32_t>(clock64()); }
 #else
 #define FA_PROF_DECL
 #define FA_PROF(slot)
 #define FA_PROF_FLUSH(base, n)
+#define FA_STAMP(step, idx)
 #endif
 
 template <int N>
@@ -293,7 +298,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               ok = mbar_wait(smem_u32(&sh.s_free[g]), j & 1, abort_flag);
               if (!ok) break;
               tc_fence_after();
+              FA_STAMP(j, 16 + g * 2)
               issue_qk(g, sn);
+              FA_STAMP(j, 17 + g * 2)
             }
           }
           if (!ok) break;
@@ -334,12 +341,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             ok = mbar_wait(smem_u32(&sh.p_full[g]), j & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
+            FA_STAMP(j, 20 + g * 2)
             const uint32_t va = smem_v + s * Cfg::kTileBytes;
 #pragma unroll
             for (int ks = 0; ks < kBlockN / 16; ++ks)
               mma_ts(tO[g], tP[g] + ks * 8, make_smem_desc(va + ks * 2048, 16384, 1024), idesc_pv,
                      j > 0 || ks > 0);
             mma_commit(smem_u32(&sh.o_full[g]));
+            FA_STAMP(j, 21 + g * 2)
           }
         }
         if (!ok) break;
@@ -417,10 +426,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         for (int grp = 0; grp < 8; ++grp) lp.finish(st[2 * grp], st[2 * grp + 1], wd + grp * 8);
       }
       FA_PROF(0)
+      if (row == 0) { FA_STAMP(j, g * 8 + 0) }
       ok = mbar_wait(smem_u32(&sh.s_full[g]), j & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       FA_PROF(1)
+      if (row == 0) { FA_STAMP(j, g * 8 + 1) }
       tc_fence_after();
       uint32_t sr[4][32];
 #pragma unroll
@@ -431,6 +442,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         mbar_arrive(smem_u32(&sh.s_free[g]));
       }
       FA_PROF(2)
+      if (row == 0) { FA_STAMP(j, g * 8 + 2) }
 
       bool need_mask = (col0 + kBlockN > sk);
       if (CAUSAL) need_mask = need_mask || (col0 + kBlockN - 1 > m0[g]);
@@ -465,6 +477,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
       const float m_new = max3(m_run, mxa, mxb);
       FA_PROF(3)
+      if (row == 0) { FA_STAMP(j, g * 8 + 3) }
 
       // The running max is only raised when it would grow by more than 2^8 in the exponent:
       // until then the stale max keeps every p below 256 and saves rescaling O.
@@ -506,11 +519,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
 
       FA_PROF(5)
+      if (row == 0) { FA_STAMP(j, g * 8 + 4) }
       // P*V of the previous tile must have finished before O is rescaled or its P buffer reused
       if (j > 0) {
         ok = mbar_wait(smem_u32(&sh.o_full[g]), (j - 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        if (row == 0) { FA_STAMP(j, g * 8 + 5) }
         tc_fence_after();
         if (__any_sync(0xffffffffu, grow)) {
           const uint64_t alpha2 = pack_f2(alpha, alpha);
@@ -537,6 +552,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       tc_fence_before();
       mbar_arrive(smem_u32(&sh.p_full[g]));
       FA_PROF(7)
+      if (row == 0) { FA_STAMP(j, g * 8 + 6) }
     }
     if (g == 0 && row == 0) { FA_PROF_FLUSH(8, n) }
 
