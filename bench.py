@@ -818,6 +818,32 @@ def extras(fc, dev, peaks, only=None):
             "fwd_pct_peak": 100 * fl / f / 1e9 / peaks["tflops"],
             "fwd_bwd_pct_peak": 100 * 3.5 * fl / (f + b) / 1e9 / peaks["tflops"]}
         del q, k, v, dout
+    # reduced cases for profiler captures (a few launches, a few hundred MB): only run when asked for by name
+    if only in ("reduced_blocksparse_fp16_d64_S4096_B1H4", "reduced_causal_bf16_d64_S16384_B1H4"):
+        B, H, d = 1, 4, 64
+        sparse = only.startswith("reduced_blocksparse")
+        S = 4096 if sparse else 16384
+        dt = torch.float16 if sparse else torch.bfloat16
+        cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=dev)
+        mk = lambda: torch.randn(B * S, H, d, device=dev, dtype=dt, generator=g)
+        q, k, v, dout = mk(), mk(), mk(), mk()
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        if sparse:
+            from flash_attn_b200.flash_blocksparse_attn_interface import convert_blockmask
+            from flash_attn_b200.sparsity_layouts import RandomLayout
+            conv = convert_blockmask(RandomLayout(0.25, seed=7).make_layout(S).to(dev), False)
+            fwd = lambda: fc.fwd_block(q, k, v, cu, cu, conv, S, S, DROPOUT_P, 0.125, False, False, None)
+            out, lse = fwd()
+            bwd = lambda: fc.bwd_block(dout, q, k, v, out, lse, dq, dk, dv, cu, cu, conv, S, S, DROPOUT_P, 0.125,
+                                       False, None)
+        else:
+            fwd = lambda: fc.fwd(q, k, v, cu, cu, S, S, 0.0, 0.125, False, True, False, None)
+            out, lse = fwd()
+            bwd = lambda: fc.bwd(dout, q, k, v, out, lse, dq, dk, dv, cu, cu, S, S, 0.0, 0.125, False, True, None)
+        f = _time_passes(fwd, 3, warmup=1)
+        b = _time_passes(bwd, 3, warmup=1)
+        res[only] = {"fwd_ms": f, "bwd_ms": b}
+        return res
     # dense attention without dropout / without the causal mask, and the cost of the deterministic dQ mode
     dense = {"dense_fp16_d64_nodropout_S4096": (8, 12, 64, 4096, torch.float16, False, 0.0),
              "dense_bf16_d128_noncausal_S4096": (16, 12, 128, 4096, torch.bfloat16, False, 0.0),

@@ -96,8 +96,14 @@ def unpad_input(hidden_states, attention_mask):
     valid token.  Returns (packed (total, dim), indices (total,), cu_seqlens (batch + 1,) int32,
     max_seqlen_in_batch int) (reference :60-80)."""
     seqlens_in_batch = attention_mask.sum(dim=-1, dtype=torch.int32)
-    indices = torch.nonzero(attention_mask.flatten(), as_tuple=False).flatten()
-    max_seqlen_in_batch = int(seqlens_in_batch.max().item())
+    # One synchronisation, which the API cannot avoid (the packed size and max_seqlen are host values):
+    # the lengths come to the host once and both are read from them; the index list is then built
+    # with a known size, which does not synchronise again (the reference pays one for `nonzero` and
+    # one for `.item()`, :70-72).
+    seqlens_host = seqlens_in_batch.cpu()
+    total = int(seqlens_host.sum())
+    max_seqlen_in_batch = int(seqlens_host.max()) if seqlens_host.numel() else 0
+    indices = torch.nonzero_static(attention_mask.flatten(), size=total).flatten()
     cu_seqlens = F.pad(torch.cumsum(seqlens_in_batch, dim=0, dtype=torch.int32), (1, 0))
     flat = hidden_states.reshape(-1, hidden_states.shape[-1])
     return index_first_axis(flat, indices), indices, cu_seqlens, max_seqlen_in_batch
