@@ -69,6 +69,24 @@ int make_tile_map(CUtensorMap* tm, const void* base, bool bf16, int64_t rows, in
   FA_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "tensor base must be 16-byte aligned");
   FA_REQUIRE((row_stride * 2) % 16 == 0 && (head_stride * 2) % 16 == 0,
              "row and head strides must be multiples of 8 elements");
+  // A descriptor is a pure function of these eight values, and a training loop presents the same
+  // ones again and again (the caching allocator hands back the same blocks): a small per-thread
+  // cache saves the driver call, which is a large share of the host time of a short-sequence call.
+  struct Entry {
+    const void* base; int64_t rows, row_stride, head_stride; int32_t heads, head_dim, box_rows, bf16;
+    CUtensorMap map;
+  };
+  constexpr int kCacheSize = 32;
+  static thread_local Entry cache[kCacheSize];
+  static thread_local int cache_used = 0, cache_next = 0;
+  for (int i = 0; i < cache_used; ++i) {
+    const Entry& e = cache[i];
+    if (e.base == base && e.rows == rows && e.row_stride == row_stride && e.head_stride == head_stride &&
+        e.heads == heads && e.head_dim == head_dim && e.box_rows == box_rows && e.bf16 == (bf16 ? 1 : 0)) {
+      *tm = e.map;
+      return FA_OK;
+    }
+  }
   cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(rows),
                         static_cast<cuuint64_t>(heads)};
   cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_stride) * 2,
@@ -81,6 +99,10 @@ int make_tile_map(CUtensorMap* tm, const void* base, bool bf16, int64_t rows, in
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  Entry& slot = cache[cache_next];
+  slot = Entry{base, rows, row_stride, head_stride, heads, head_dim, box_rows, bf16 ? 1 : 0, *tm};
+  cache_next = (cache_next + 1) % kCacheSize;
+  if (cache_used < kCacheSize) ++cache_used;
   return FA_OK;
 }
 

@@ -6,6 +6,7 @@ PyTorch is used here only for device memory (output / scratch allocation through
 allocator), the current stream and the default CUDA generator's Philox state.
 """
 import ctypes
+import struct
 
 import torch
 
@@ -119,8 +120,22 @@ def _philox_state(gen, increment):
     return seed, offset
 
 
+_DIMS_OK = (16, 32, 64, 128)
+
+
 def _check_qkv(q, k, v, cu_seqlens_q, cu_seqlens_k):
+    """Argument checks of mha_fwd / mha_bwd (csrc/flash_attn/fmha_api.cpp:199-230).  The usual, valid
+    call is decided by one expression; only a call that fails it is taken apart for its message."""
+    qs, ks, vs = q.shape, k.shape, v.shape
     dt = q.dtype
+    nb = cu_seqlens_q.shape[0]
+    if (len(qs) == 3 and ks[1:] == qs[1:] and vs == ks and q.is_cuda and k.is_cuda and v.is_cuda
+            and (dt is torch.float16 or dt is torch.bfloat16) and k.dtype is dt and v.dtype is dt
+            and cu_seqlens_q.dtype is torch.int32 and cu_seqlens_k.dtype is torch.int32
+            and cu_seqlens_q.is_cuda and cu_seqlens_k.is_cuda and nb > 1 and cu_seqlens_k.shape[0] == nb
+            and qs[2] in _DIMS_OK and q.stride(2) == 1 and k.stride(2) == 1 and v.stride(2) == 1
+            and cu_seqlens_q.is_contiguous() and cu_seqlens_k.is_contiguous()):
+        return nb - 1, qs[0], ks[0], qs[1], qs[2]
     _require(q.is_cuda and k.is_cuda and v.is_cuda, "q, k, v must be CUDA tensors")
     _require(dt is torch.float16 or dt is torch.bfloat16, "q must be fp16 or bf16")
     _require(k.dtype is dt and v.dtype is dt, "q, k, v must have the same dtype")
@@ -129,38 +144,65 @@ def _check_qkv(q, k, v, cu_seqlens_q, cu_seqlens_k):
     _require(cu_seqlens_q.is_cuda and cu_seqlens_k.is_cuda, "cu_seqlens must be CUDA tensors")
     _require(cu_seqlens_q.is_contiguous() and cu_seqlens_k.is_contiguous(),
              "cu_seqlens must be contiguous")
-    qs, ks, vs = q.shape, k.shape, v.shape
     _require(len(qs) == 3 and len(ks) == 3 and len(vs) == 3, "q, k, v must be (total, heads, d)")
     _require(q.stride(2) == 1 and k.stride(2) == 1 and v.stride(2) == 1,
              "q, k, v must have a contiguous last dimension")
-    batch = cu_seqlens_q.shape[0] - 1
+    batch = nb - 1
     _require(batch > 0, "batch size must be positive")
     _require(cu_seqlens_k.shape[0] == batch + 1, "cu_seqlens_q / cu_seqlens_k size mismatch")
     total_q, heads, d = qs
     total_k = ks[0]
-    _require(d in (16, 32, 64, 128), "head_dim must be 16, 32, 64 or 128")
+    _require(d in _DIMS_OK, "head_dim must be 16, 32, 64 or 128")
     _require(ks[1] == heads and ks[2] == d, "k has the wrong shape")
     _require(vs[0] == total_k and vs[1] == heads and vs[2] == d, "v has the wrong shape")
     return batch, total_q, total_k, heads, d
 
 
-def _make_fwd(dims, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout, scale, causal, seed, offset):
-    """FwdParams filled through the structure's positional constructor (one call instead of forty
-    attribute stores): the per-call host time of short-sequence workloads is mostly this binding."""
+# struct fa_fwd_params / fa_bwd_params as `struct` formats (native alignment): packing forty values into
+# a buffer in one call costs a third of the ctypes constructor, and the per-call host time of
+# short-sequence workloads is mostly this binding.
+_FWD_FMT = "9P 2q 9q 7i 2f 2i 2Q 2i P P N 2i"
+_FWD_PACK = struct.Struct("@" + _FWD_FMT)
+_BWD_PACK = struct.Struct("@" + _FWD_FMT + " 5P 6q P N 2i")
+assert _FWD_PACK.size == ctypes.sizeof(FwdParams), (_FWD_PACK.size, ctypes.sizeof(FwdParams))
+assert _BWD_PACK.size == ctypes.sizeof(BwdParams), (_BWD_PACK.size, ctypes.sizeof(BwdParams))
+
+
+def _fwd_values(dims, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout, scale, causal, seed, offset):
     batch, total_q, total_k, heads, d = dims
     qs, ks, vs, os_ = q.stride(), k.stride(), v.stride(), o.stride()
     mh = options.mask_heads
     if mh is not None:
         _require(mh[0] >= mh[1] + heads and mh[1] >= 0,
                  "head_shard: heads_total must cover head_offset + heads of this call")
-    mh_total, mh_offset = mh if mh is not None else (0, 0)
-    return FwdParams(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
-                     cu_q.data_ptr(), cu_k.data_ptr(), None, None, 0, 0,
-                     qs[0], qs[1], ks[0], ks[1], vs[0], vs[1], os_[0], os_[1], lse.shape[-1],
-                     batch, heads, d, total_q, total_k, int(max_q), int(max_k),
-                     float(p_dropout), float(scale), 1 if causal else 0,
-                     1 if q.dtype is torch.bfloat16 else 0, seed, offset, mh_total, mh_offset,
-                     _status_buffer(q.device).data_ptr(), None, 0, 0, 0)
+        mh_total, mh_offset = mh
+    else:
+        mh_total = mh_offset = 0
+    return (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+            cu_q.data_ptr(), cu_k.data_ptr(), 0, 0, 0, 0,
+            qs[0], qs[1], ks[0], ks[1], vs[0], vs[1], os_[0], os_[1], lse.shape[-1],
+            batch, heads, d, total_q, total_k, int(max_q), int(max_k),
+            float(p_dropout), float(scale), 1 if causal else 0,
+            1 if q.dtype is torch.bfloat16 else 0, seed, offset, mh_total, mh_offset,
+            _status_buffer(q.device).data_ptr(), 0, 0, 0, 0)
+
+
+def _make_fwd(dims, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout, scale, causal, seed, offset):
+    """A filled FwdParams (a view of one packed buffer)."""
+    buf = bytearray(_FWD_PACK.size)
+    _FWD_PACK.pack_into(buf, 0, *_fwd_values(dims, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout,
+                                             scale, causal, seed, offset))
+    return FwdParams.from_buffer(buf)
+
+
+def _make_bwd(fwd_values, dout, dq, dk, dv, softmax_d, ws, stage_mask, deterministic):
+    """A filled BwdParams: the forward block followed by the gradient pointers and strides."""
+    dqs, dks, dvs = dq.stride(), dk.stride(), dv.stride()
+    buf = bytearray(_BWD_PACK.size)
+    _BWD_PACK.pack_into(buf, 0, *fwd_values, dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                        softmax_d.data_ptr(), dqs[0], dqs[1], dks[0], dks[1], dvs[0], dvs[1],
+                        ws.data_ptr(), ws.numel(), stage_mask, deterministic)
+    return BwdParams.from_buffer(buf)
 
 
 def _fill_fwd(p, dims, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout, scale, causal, seed, offset):
@@ -317,13 +359,10 @@ def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
         det = 1 if options.deterministic else 0
         nbytes = lib.fa_bwd_workspace_bytes_ex(total_q, heads, d, batch, int(max_seqlen_q), det)
         ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
-        dqs, dks, dvs = dq.stride(), dk.stride(), dv.stride()
-        p = BwdParams(_make_fwd((batch, total_q, total_k, heads, d), q, k, v, out, softmax_lse,
-                                cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout,
-                                softmax_scale, is_causal, seed, offset),
-                      dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), softmax_d.data_ptr(),
-                      dqs[0], dqs[1], dks[0], dks[1], dvs[0], dvs[1], ws.data_ptr(), ws.numel(),
-                      _stage_mask, det)
+        p = _make_bwd(_fwd_values((batch, total_q, total_k, heads, d), q, k, v, out, softmax_lse,
+                                  cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout,
+                                  softmax_scale, is_causal, seed, offset),
+                      dout, dq, dk, dv, softmax_d, ws, _stage_mask, det)
         if _blockmask is not None:
             _check_blockmask(_blockmask, max_seqlen_q, max_seqlen_k, q)
             bws = _bs_workspace(q.device, batch, _blockmask)

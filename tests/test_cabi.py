@@ -88,3 +88,22 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert b"head_dim" in _lib.lib.fa_last_error()
     bp = _lib.BwdParams()
     assert _lib.lib.fa_bwd(ctypes.byref(bp), None) == _lib.FA_ERR_INVALID_ARGUMENT
+
+
+def test_packed_parameter_buffers_match_the_structures():
+    """The binding fills fa_fwd_params / fa_bwd_params by packing all values into a buffer in one call;
+    every value must land in the field the ctypes structure (and so the header) gives it."""
+    from flash_attn_b200 import _lib
+    from flash_attn_b200 import flash_attn_cuda as fc
+    vals = list(range(1, 41))
+    vals[27], vals[28] = 0.5, 0.25          # p_dropout, softmax_scale
+    buf = bytearray(fc._FWD_PACK.size)
+    fc._FWD_PACK.pack_into(buf, 0, *vals)
+    p = _lib.FwdParams.from_buffer(buf)
+    assert [(getattr(p, name) or 0) for name, _ in _lib.FwdParams._fields_] == vals
+    tail = list(range(41, 56))
+    buf = bytearray(fc._BWD_PACK.size)
+    fc._BWD_PACK.pack_into(buf, 0, *(vals + tail))
+    pb = _lib.BwdParams.from_buffer(buf)
+    assert [(getattr(pb, name) or 0) for name, _ in _lib.BwdParams._fields_[1:]] == tail
+    assert pb.fwd.blockmask_cols == 40 and pb.fwd.q == 1
