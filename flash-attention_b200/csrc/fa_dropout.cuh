@@ -195,6 +195,65 @@ struct LanePhilox {
   }
 };
 
+// ---------------------------------------------------------------------------------------------
+// Quad-per-thread mask generation (the layout of the tcgen05.ld 16x256b shape: thread t of a warp
+// working on a 16-row block holds rows t/4 and t/4 + 8 and, of every 16-column group, columns 2q,
+// 2q+1, 2q+8, 2q+9 with q = t % 4).  Those eight values are the eight 16-bit outputs of ONE Philox
+// call whose subsequence ends in (group % 8) * 32 + t: a thread runs whole calls, nothing is
+// exchanged, and the multipliers stay immediates.
+//
+// Two of the fourteen wide multiplies of a call do not depend on the call.  With the state
+// (c0, c1, c2, c3) = (counter low, counter high, subsequence low, subsequence high):
+//   round 0   M1 * c2 depends on the subsequence only (computed once per kernel and group),
+//             M0 * c0 on the counter only (once per tile);
+//   round 1   its word-2 input hi(M0 * c0) ^ c3 ^ key1 is the same for every call of a tile
+//             (the subsequence's high word is per (batch, head)), so M1 * that is per tile too.
+// A call therefore starts at round 1 with one multiply, then runs rounds 2..6: 11 multiplies.
+struct QuadPhilox {
+  uint32_t a_hi[8], b_lo[8];  // per 16-column group of a tile: hi(M1 * sub) ^ key0[0], lo(M1 * sub)
+  uint32_t sub_hi;
+  // per (tile, 16-row block)
+  uint32_t c1, n3k, w_hi, w_lo;
+
+  __device__ __forceinline__ void init(const DropoutParams& dp, int64_t bh_sub, int lane) {
+    // bh_sub is a multiple of 256 and group * 32 + lane < 256: the sum never carries
+    const uint32_t sub_lo = static_cast<uint32_t>(bh_sub) + static_cast<uint32_t>(lane);
+    sub_hi = static_cast<uint32_t>(static_cast<uint64_t>(bh_sub) >> 32);
+#pragma unroll
+    for (int grp = 0; grp < 8; ++grp) {
+      const uint64_t v = mul_wide_u32(0xCD9E8D57u, sub_lo + grp * 32);
+      a_hi[grp] = static_cast<uint32_t>(v >> 32) ^ dp.rk0[0];
+      b_lo[grp] = static_cast<uint32_t>(v);
+    }
+  }
+  // Counter of the calls of one 128-column tile for one 16-row block (see fa_dropout_words).
+  __device__ __forceinline__ void set_tile(const DropoutParams& dp, int64_t iter_index, int32_t col0) {
+    const int32_t n_mask = (1 << dp.n_shift) - 1;
+    const uint64_t ctr = dp.counter_base + static_cast<uint64_t>(iter_index << (dp.n_shift - 7)) +
+                         static_cast<uint64_t>((col0 & n_mask) >> 7);
+    c1 = static_cast<uint32_t>(ctr >> 32);
+    const uint64_t u = mul_wide_u32(0xD2511F53u, static_cast<uint32_t>(ctr));
+    const uint32_t n2 = static_cast<uint32_t>(u >> 32) ^ sub_hi ^ dp.rk1[0];
+    n3k = static_cast<uint32_t>(u) ^ dp.rk1[1];
+    const uint64_t w = mul_wide_u32(0xCD9E8D57u, n2);
+    w_hi = static_cast<uint32_t>(w >> 32) ^ dp.rk0[1];
+    w_lo = static_cast<uint32_t>(w);
+  }
+  // State after rounds 0 and 1 of the call for 16-column group `grp` of the tile.
+  __device__ __forceinline__ void start(int grp, uint32_t (&s)[4]) const {
+    const uint64_t p = mul_wide_u32(0xD2511F53u, a_hi[grp] ^ c1);
+    s[0] = w_hi ^ b_lo[grp];
+    s[1] = w_lo;
+    s[2] = static_cast<uint32_t>(p >> 32) ^ n3k;
+    s[3] = static_cast<uint32_t>(p);
+  }
+  // Rounds 2..6; afterwards s[0], s[1] are the keep words of row t/4 (columns 2q, 2q+1 and 2q+8,
+  // 2q+9; low half = even column) and s[2], s[3] those of row t/4 + 8.
+  static __device__ __forceinline__ void round(const DropoutParams& dp, uint32_t (&s)[4], int r) {
+    philox_round(s, dp.rk0[r], dp.rk1[r]);
+  }
+};
+
 // Keep factors (1.0f kept / 0.0f dropped) of the two 16-bit values of a keep word, without integer
 // compares: the 16 bits become the top mantissa bits of a float in [0.5, 2) (bytes 0x3F | hi | lo |
 // filler, a monotone map), and a saturating fma against the threshold mapped the same way gives

@@ -2,7 +2,9 @@
 //
 // One CTA owns two consecutive 128-row query tiles of one (batch, head) pair and walks the key /
 // value sequence in 128-row tiles.  Warp roles:
-//   warps 0-3   softmax group 0 (query tile 0): one thread per query row
+//   warps 0-3   softmax group 0 (query tile 0): one thread per query row; with dropout a thread
+//               holds two rows of each of the warp's two 16-row blocks and a quarter of their
+//               columns (the ownership pattern of the reference's mask generator)
 //   warps 4-7   softmax group 1 (query tile 1)
 //   warp  8     TMA producer (Q once, K/V ring)
 //   warp  9     tcgen05.mma issuer (d = 128: every product; d = 64: S = Q K^T only)
@@ -92,6 +94,44 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   } else {
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+// Epilogue of one query row (thread = row, 32x32b shape): O = acc / (sum * p_keep) in the 16-bit
+// type, LSE = max * scale + ln(sum); a row without any valid key gets zeros and -inf.
+template <int D, bool BF16>
+__device__ __forceinline__ void store_rows(const KernelArgs& a, uint32_t tO, bool have_acc, bool ok, int ig,
+                                           int sq, int q_start, int b, int h, float m_run, float l_run) {
+  const bool bad_sum = (l_run == 0.f) || (l_run != l_run);
+  const float inv = bad_sum ? 1.f : (1.f / l_run) * a.rp_keep;
+  const bool store_row = ok && (ig < sq);
+  uint16_t* orow = reinterpret_cast<uint16_t*>(a.o) + static_cast<int64_t>(q_start + ig) * a.o_row_stride +
+                   static_cast<int64_t>(h) * a.o_head_stride;
+#pragma unroll
+  for (int c = 0; c < D / 32; ++c) {
+    uint32_t orr[32];
+    if (have_acc) {
+      tmem_ld32(tO + c * 32, orr);
+      tmem_wait_ld();
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) orr[i] = 0u;
+    }
+    if (store_row && c * 32 < a.head_dim) {
+      uint32_t pko[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        pko[i] = pack_lowp<BF16>(__uint_as_float(orr[2 * i]) * inv, __uint_as_float(orr[2 * i + 1]) * inv);
+      uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+      const int nvec = min(4, (a.head_dim - c * 32) / 8);
+#pragma unroll
+      for (int v = 0; v < 4; ++v)
+        if (v < nvec) dst[v] = make_uint4(pko[4 * v], pko[4 * v + 1], pko[4 * v + 2], pko[4 * v + 3]);
+    }
+  }
+  if (store_row) {
+    const float lse = bad_sum ? -INFINITY : (m_run * a.scale + __logf(l_run));
+    a.lse[(static_cast<int64_t>(b) * a.heads + h) * a.lse_stride + ig] = lse;
   }
 }
 
@@ -355,8 +395,218 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         mma_commit(smem_u32(&sh.v_empty[s]));
       }
     }
+  } else if (warp < 8 && DROPOUT) {
+    // ------------------------------------------------------------------ softmax groups, dropout
+    // Quad layout: a warp reads its 32 rows as two 16-row blocks (hh) with the 16x256b shape, so a
+    // thread holds rows r8 and r8 + 8 of each block and, of every 8-column unit, two adjacent columns.
+    // That is the ownership pattern of the reference's mask generator: one Philox call covers exactly
+    // one thread's part of a 16 x 16 patch (QuadPhilox).  Row statistics are reduced over the four
+    // lanes of a quad.  Row index ri = hh * 2 + u for row r8 + 16 * hh + 8 * u of the warp.
+    reg_alloc<224>();
+    const int g = warp >> 2;
+    const int wq = warp & 3;
+    const int r8 = lane >> 2, q4 = lane & 3;
+    const int row_base = m0[g] + wq * 32 + r8;  // + 16 * hh + 8 * u: query index within the sequence
+    const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
+    constexpr uint32_t kHalf = 16u << 16;  // second 16-row block of the warp
+    const uint32_t tS = tmem + (g == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1) + lane_sel;
+    const uint32_t tO = tmem + (g == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1) + lane_sel;
+    const uint32_t tP = tmem + (g == 0 ? Cfg::kTmemP0 : Cfg::kTmemP1) + lane_sel;
+    const int n = n_tiles[g];
+    const bool active = m0[g] < sq;
+
+    float m_run[4], l_run[4];  // l_run: this thread's share of the row sum (its 32 columns per tile)
+#pragma unroll
+    for (int ri = 0; ri < 4; ++ri) { m_run[ri] = -INFINITY; l_run[ri] = 0.f; }
+    bool ok = true;
+    const uint64_t c2 = pack_f2(a.scale_log2, a.scale_log2);
+
+    const int64_t bh_sub =
+        (static_cast<int64_t>(b) * a.drop.heads_total + a.drop.head_offset + h) * 256;
+    const int L16 = (sq + 15) >> 4;
+    const int i16_base = (m0[g] + wq * 32) >> 4;  // 16-row block index of hh = 0
+    QuadPhilox qp;
+    qp.init(a.drop, bh_sub, lane);
+    const float thr_term = fa_keep_thr_term(a.drop.threshold);
+
+    for (int j = 0; j < n && ok; ++j) {
+      const int col0 = kv_tile(j) * kBlockN;
+      int32_t bs_it[2] = {0, 0};
+      if constexpr (BLOCKSPARSE) {
+        const int kb = col0 >> 8;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh)
+          bs_it[hh] = (i16_base + hh) < a.bs_rows16
+                          ? a.bs_iter[(static_cast<int64_t>(b) * a.bs_kblocks + kb) * a.bs_rows16 + i16_base + hh]
+                          : -1;
+      }
+      bool need_mask = (col0 + kBlockN > sk);
+      if (CAUSAL) need_mask = need_mask || (col0 + kBlockN - 1 > m0[g]);
+      float alpha[4];
+      bool grow_any = false;
+      // pk[hh][2 * unit + u]: the 16x128b register of (row u, packed column pair 4 * unit + q4)
+      uint32_t pk[2][32];
+      // The two 16-row blocks of the warp one after the other (their rows are independent), which
+      // keeps the live registers at one block of keep words, scores and packed probabilities.
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        // Keep words of the block: 8 calls (one per 16-column group), rounds interleaved so that their
+        // multiply chains overlap.  kw[grp][2 * u + half]: row u, columns 16 grp + 8 half + 2 q4 (+1 in
+        // the high 16 bits).  One iteration index per tile: a 128-column tile lies inside one key block.
+        uint32_t kw[8][4];
+        {
+          int64_t it_index;
+          if constexpr (BLOCKSPARSE) it_index = bs_it[hh];
+          else it_index = fa_iter_index(CAUSAL, col0 >> a.drop.n_shift, i16_base + hh, L16, a.drop.n_shift);
+          qp.set_tile(a.drop, it_index, col0);
+#pragma unroll
+          for (int grp = 0; grp < 8; ++grp) qp.start(grp, kw[grp]);
+#pragma unroll
+          for (int r = 2; r < 7; ++r)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) QuadPhilox::round(a.drop, kw[k], r);
+        }
+        if (hh == 0) {
+          ok = mbar_wait(smem_u32(&sh.s_full[g]), j & 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        // sr[4 * unit + 2 * u + c]: row u of the block, column 8 * unit + 2 * q4 + c of the tile
+        uint32_t sr[64];
+        tmem_ld_quad64(tS + hh * kHalf, sr);
+        tmem_wait_ld();
+        if constexpr (Cfg::kSeparateP) {
+          if (hh == 1) {
+            tc_fence_before();
+            mbar_arrive(smem_u32(&sh.s_free[g]));
+          }
+        }
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const int col = col0 + (i >> 2) * 8 + 2 * q4 + (i & 1);
+            const int ig = row_base + hh * 16 + ((i >> 1) & 1) * 8;
+            bool valid = col < sk;
+            if (CAUSAL) valid = valid && (col <= ig);
+            if (!valid) sr[i] = __float_as_uint(-INFINITY);
+          }
+        }
+        if constexpr (BLOCKSPARSE) {
+          // a 16-row block that is not in the layout for this 256-column key block sees -inf
+          if (bs_it[hh] < 0) {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) sr[i] = __float_as_uint(-INFINITY);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int ri = hh * 2 + u;
+          // row maximum: 32 own columns, then the quad
+          float mxa = -INFINITY, mxb = -INFINITY;
+#pragma unroll
+          for (int unit = 0; unit < 16; unit += 2) {
+            mxa = max3(mxa, __uint_as_float(sr[4 * unit + 2 * u]), __uint_as_float(sr[4 * unit + 2 * u + 1]));
+            mxb = max3(mxb, __uint_as_float(sr[4 * unit + 4 + 2 * u]), __uint_as_float(sr[4 * unit + 5 + 2 * u]));
+          }
+          float mx = fmaxf(mxa, mxb);
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+          const float m_new = fmaxf(m_run[ri], mx);
+          // The running max is only raised when it would grow by more than 2^8 in the exponent:
+          // until then the stale max keeps every p below 256 and saves rescaling O.
+          const bool grow = (m_new - m_run[ri]) * a.scale_log2 > 8.f;
+          const float m_next = grow ? m_new : m_run[ri];
+          alpha[ri] = (!grow || m_run[ri] == -INFINITY) ? (grow ? 0.f : 1.f)
+                                                        : ex2f((m_run[ri] - m_new) * a.scale_log2);
+          m_run[ri] = m_next;
+          const float mc = (m_next == -INFINITY) ? 0.f : m_next * a.scale_log2;
+          grow_any = grow_any || grow;
+
+          // p = exp2(s * c - m * c): packed fma, one ex2 per element, packed row sum; the row sum
+          // takes the un-dropped p, P*V takes p times the keep factor (1 or 0), rounded to 16 bits
+          const uint64_t nmc2 = pack_f2(-mc, -mc);
+          uint64_t sum_a = 0ull, sum_b = 0ull;
+#pragma unroll
+          for (int unit = 0; unit < 16; unit += 2) {
+            float p0, p1, p2, p3;
+            unpack_f2(fma2(pack_f2(__uint_as_float(sr[4 * unit + 2 * u]), __uint_as_float(sr[4 * unit + 2 * u + 1])), c2, nmc2), p0, p1);
+            unpack_f2(fma2(pack_f2(__uint_as_float(sr[4 * unit + 4 + 2 * u]), __uint_as_float(sr[4 * unit + 5 + 2 * u])), c2, nmc2), p2, p3);
+            p0 = ex2f(p0); p1 = ex2f(p1); p2 = ex2f(p2); p3 = ex2f(p3);
+            const uint64_t p01 = pack_f2(p0, p1), p23 = pack_f2(p2, p3);
+            sum_a = add2(sum_a, p01);
+            sum_b = add2(sum_b, p23);
+            const uint32_t w01 = kw[unit / 2][2 * u], w23 = kw[unit / 2][2 * u + 1];
+            unpack_f2(mul2(p01, pack_f2(fa_keep_factor_lo(w01, thr_term), fa_keep_factor_hi(w01, thr_term))), p0, p1);
+            unpack_f2(mul2(p23, pack_f2(fa_keep_factor_lo(w23, thr_term), fa_keep_factor_hi(w23, thr_term))), p2, p3);
+            pk[hh][2 * unit + u] = pack_lowp<BF16>(p0, p1);
+            pk[hh][2 * unit + 2 + u] = pack_lowp<BF16>(p2, p3);
+          }
+          float s0, s1;
+          unpack_f2(add2(sum_a, sum_b), s0, s1);
+          l_run[ri] = l_run[ri] * alpha[ri] + (s0 + s1);
+        }
+      }
+      if (!ok) break;
+
+      // P*V of the previous tile must have finished before O is rescaled or its P buffer reused
+      if (j > 0) {
+        ok = mbar_wait(smem_u32(&sh.o_full[g]), (j - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, grow_any)) {
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const uint64_t al0 = pack_f2(alpha[hh * 2], alpha[hh * 2]);
+            const uint64_t al1 = pack_f2(alpha[hh * 2 + 1], alpha[hh * 2 + 1]);
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c) {
+              uint32_t orr[32];
+              tmem_ld_quad32(tO + hh * kHalf + c * 64, orr);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                float lo, hi;
+                unpack_f2(mul2(pack_f2(__uint_as_float(orr[i]), __uint_as_float(orr[i + 1])), (i & 2) ? al1 : al0), lo, hi);
+                orr[i] = __float_as_uint(lo);
+                orr[i + 1] = __float_as_uint(hi);
+              }
+              tmem_st_quad32(tO + hh * kHalf + c * 64, orr);
+            }
+          }
+        }
+      }
+      // hand P to the tensor core through tensor memory
+      tmem_st_pair32(tP, pk[0]);
+      tmem_st_pair32(tP + kHalf, pk[1]);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sh.p_full[g]));
+    }
+
+    // ---------------- epilogue: O = acc / (sum * p_keep), LSE, one thread per query row again
+    if (active) {
+      if (n > 0 && ok) {
+        ok = mbar_wait(smem_u32(&sh.o_full[g]), (n - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        tc_fence_after();
+      }
+      // row lane (0..31 of the warp) = 16 * hh + 8 * u + r8: its statistics sit in the quad r8 under ri = lane / 8
+      float m_row = -INFINITY, l_row = 0.f;
+#pragma unroll
+      for (int ri = 0; ri < 4; ++ri) {
+        float l = l_run[ri];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const float l_src = __shfl_sync(0xffffffffu, l, (lane & 7) * 4);
+        const float m_src = __shfl_sync(0xffffffffu, m_run[ri], (lane & 7) * 4);
+        if ((lane >> 3) == ri) { l_row = l_src; m_row = m_src; }
+      }
+      store_rows<D, BF16>(a, tO, n > 0 && ok, ok, m0[g] + wq * 32 + lane, sq, q_start, b, h, m_row, l_row);
+    }
   } else if (warp < 8) {
-    // ------------------------------------------------------------------ softmax groups
+    // ------------------------------------------------------------------ softmax groups, no dropout
     reg_alloc<224>();
     const int g = warp >> 2;
     const int row = tid & 127;
@@ -371,18 +621,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     const uint64_t c2 = pack_f2(a.scale_log2, a.scale_log2);
-
-    // dropout: per-lane generator state (a lane and its partner 8 lanes away own rows r and r + 8 of
-    // one 16-row block, which share every Philox call; each runs half of the calls)
-    const int64_t bh_sub =
-        (static_cast<int64_t>(b) * a.drop.heads_total + a.drop.head_offset + h) * 256;
-    const int L16 = (sq + 15) >> 4;
-    LanePhilox lp;
-    float thr_term = 0.f;
-    if constexpr (DROPOUT) {
-      lp.init(a.drop, bh_sub, ig);
-      thr_term = fa_keep_thr_term(a.drop.threshold);
-    }
 
 #ifdef FA_FWD_OFFSET
     // experiment: start query tile 1 half a tile period behind query tile 0
@@ -400,30 +638,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         bs_it = (ig >> 4) < a.bs_rows16
                     ? a.bs_iter[(static_cast<int64_t>(b) * a.bs_kblocks + kb) * a.bs_rows16 + (ig >> 4)]
                     : -1;
-      }
-      // Dropout: the keep words of the tile (wd[p] covers columns 2p, 2p + 1) do not depend on the
-      // scores, so they are drawn before the wait for S.
-      uint32_t wd[DROPOUT ? 64 : 1];
-      if constexpr (DROPOUT) {
-        // one iteration index per tile: a 128-column tile lies inside one key block
-        int64_t it_index;
-        if constexpr (BLOCKSPARSE) it_index = bs_it;
-        else it_index = fa_iter_index(CAUSAL, col0 >> a.drop.n_shift, ig >> 4, L16, a.drop.n_shift);
-        lp.set_tile(a.drop, it_index, col0);
-        // 16 independent calls (8 column groups x 2 quarters), rounds interleaved so that the
-        // multiply chains of different calls overlap
-        uint32_t st[16][4];
-#pragma unroll
-        for (int grp = 0; grp < 8; ++grp) {
-          lp.start(grp, 0, st[2 * grp]);
-          lp.start(grp, 1, st[2 * grp + 1]);
-        }
-#pragma unroll
-        for (int r = 0; r < 7; ++r)
-#pragma unroll
-          for (int k = 0; k < 16; ++k) lp.round(st[k], r);
-#pragma unroll
-        for (int grp = 0; grp < 8; ++grp) lp.finish(st[2 * grp], st[2 * grp + 1], wd + grp * 8);
       }
       FA_PROF(0)
       if (row == 0) { FA_STAMP(j, g * 8 + 0) }
@@ -503,12 +717,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           const uint64_t p01 = pack_f2(p0, p1), p23 = pack_f2(p2, p3);
           sum_a = add2(sum_a, p01);
           sum_b = add2(sum_b, p23);
-          if constexpr (DROPOUT) {
-            // the row sum takes the un-dropped p; P*V takes p times the keep factor (1 or 0)
-            const uint32_t w01 = wd[c * 16 + i / 2], w23 = wd[c * 16 + i / 2 + 1];
-            unpack_f2(mul2(p01, pack_f2(fa_keep_factor_lo(w01, thr_term), fa_keep_factor_hi(w01, thr_term))), p0, p1);
-            unpack_f2(mul2(p23, pack_f2(fa_keep_factor_lo(w23, thr_term), fa_keep_factor_hi(w23, thr_term))), p2, p3);
-          }
           pk[c * 16 + i / 2] = pack_lowp<BF16>(p0, p1);
           pk[c * 16 + i / 2 + 1] = pack_lowp<BF16>(p2, p3);
         }
@@ -563,38 +771,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
       }
-      const bool bad_sum = (l_run == 0.f) || (l_run != l_run);
-      const float inv = bad_sum ? 1.f : (1.f / l_run) * a.rp_keep;
-      const bool store_row = ok && (ig < sq);
-      uint16_t* orow = reinterpret_cast<uint16_t*>(a.o) +
-                       static_cast<int64_t>(q_start + ig) * a.o_row_stride +
-                       static_cast<int64_t>(h) * a.o_head_stride;
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t orr[32];
-        if (n > 0 && ok) {
-          tmem_ld32(tO + c * 32, orr);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) orr[i] = 0u;
-        }
-        if (store_row && c * 32 < a.head_dim) {
-          uint32_t pko[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i)
-            pko[i] = pack_lowp<BF16>(__uint_as_float(orr[2 * i]) * inv, __uint_as_float(orr[2 * i + 1]) * inv);
-          uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
-          const int nvec = min(4, (a.head_dim - c * 32) / 8);
-#pragma unroll
-          for (int v = 0; v < 4; ++v)
-            if (v < nvec) dst[v] = make_uint4(pko[4 * v], pko[4 * v + 1], pko[4 * v + 2], pko[4 * v + 3]);
-        }
-      }
-      if (store_row) {
-        const float lse = bad_sum ? -INFINITY : (m_run * a.scale + __logf(l_run));
-        a.lse[(static_cast<int64_t>(b) * a.heads + h) * a.lse_stride + ig] = lse;
-      }
+      store_rows<D, BF16>(a, tO, n > 0 && ok, ok, ig, sq, q_start, b, h, m_run, l_run);
     }
   }
 
