@@ -16,8 +16,9 @@ copied out inside the timed region, `roofline` for the dominant kernel (backward
 against the measured tensor-core peak, `cpu_baseline` = the CPU oracle (standard attention in
 fp32) timed on a bounded sample on this host.  With N > 1 (one process per GPU under torchrun)
 every rank runs its own batch shard (weak scaling, no data-path collective) and the outputs are
-re-assembled with one NCCL all-gather per pass, on a side stream with few CTAs so that it does not
-displace the attention kernels; `ms_per_step_no_gather` is the same loop without it.  The line also
+re-assembled on every rank with asynchronous peer copies over NVLink (copy engines, no kernel: an
+all-gather kernel would take SMs from attention kernels that want all of them), on a side stream;
+`ms_per_step_no_gather` is the same loop without the re-assembly.  The line also
 carries `long_context` (batch 2 x 32 heads x 65536, causal, bf16: this rank's 32 / N heads, forward +
 backward, with and without the all-gather of the outputs over NVLink) and `causal_lm_d128_S4096`.
 """
@@ -193,7 +194,7 @@ def workload_config(args, lengths):
                         % (BATCH, HEADS, HEAD_DIM, args.seqlen, DROPOUT_P),
             "batch_per_gpu": BATCH, "heads": HEADS, "head_dim": HEAD_DIM, "max_seqlen": args.seqlen,
             "total_tokens_per_gpu": int(sum(lengths)), "dropout_p": DROPOUT_P, "causal": False,
-            "parallelism": "batch shards, one per GPU; outputs all-gathered",
+            "parallelism": "batch shards, one per GPU; outputs re-assembled on every rank by peer copies",
             "l2": "working set (qkv, dout, out, dqkv, fp32 dq accumulator) exceeds the 126 MB L2"}
 
 
@@ -234,8 +235,8 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        # The only collective is the re-assembly of outputs, which runs beside attention kernels that
-        # want every SM: keep NCCL's kernels to a few CTAs.
+        # Collectives (the head-shard gather of the long-context block) run beside attention kernels
+        # that want every SM: keep NCCL's kernels to a few CTAs.
         os.environ.setdefault("NCCL_MAX_CTAS", "4")
         dist.init_process_group("nccl", device_id=dev)
 
@@ -261,22 +262,21 @@ def main():
     torch.cuda.manual_seed(1234)
     side = torch.cuda.Stream(device=dev)
 
-    gathered = torch.empty((world * total, HEADS, HEAD_DIM), dtype=torch.float16, device=dev) if world > 1 else None
+    # Re-assembly of the outputs of all ranks: every rank writes its shard into the receive buffers of
+    # the others with asynchronous peer copies (copy engines over NVLink, no kernel), on a side stream.
+    reassembly = parallel.PeerTokenGather((total, HEADS, HEAD_DIM), torch.float16, dev) if world > 1 else None
 
     def one_pass(gather):
         """forward + backward through the extension-module contract (C ABI), data in HBM."""
         out, lse, seed, offset = fc.fwd(q, k, v, cu, cu, max_s, max_s, DROPOUT_P, scale, False, False, False,
                                         None, return_philox=True)
         if gather:
-            # re-assembly of the outputs of all ranks, ordered by streams only (no host wait)
+            # ordered by streams only (no host wait); the copies of pass i may still run during pass i + 1
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                out.record_stream(side)
-                dist.all_gather_into_tensor(gathered, out)
+                reassembly.gather(out)
         fc.bwd(dout, q, k, v, out, lse, dqkv[:, 0], dqkv[:, 1], dqkv[:, 2], cu, cu, max_s, max_s,
                DROPOUT_P, scale, False, False, None, philox=(seed, offset))
-        if gather:
-            torch.cuda.current_stream().wait_stream(side)
         return out
 
     state = {"passes": 1}
@@ -284,6 +284,8 @@ def main():
     def step_resident():
         for _ in range(state["passes"]):
             one_pass(world > 1)
+        if world > 1:
+            torch.cuda.current_stream().wait_stream(side)   # a step ends when its last shard has been delivered
 
     def step_no_gather():
         for _ in range(state["passes"]):

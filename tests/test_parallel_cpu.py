@@ -28,6 +28,12 @@ def _worker(rank, world, port, ok):
         assert torch.equal(finish(), full)
         tok = full[rank * 10:(rank + 1) * 10].contiguous()
         assert torch.equal(parallel.all_gather_tokens(tok), full[:10 * world])
+        # the copy-engine reassembly falls back to the collective without CUDA: same result
+        pg = parallel.PeerTokenGather(tok.shape, tok.dtype, tok.device)
+        assert not pg.uses_copy_engines
+        pg.gather(tok)
+        pg.wait()
+        assert torch.equal(pg.buffer.view(-1, 8, 16), full[:10 * world])
         try:
             parallel.shard_heads(torch.zeros(3, 5, 4), world, rank)
             raise AssertionError("expected ValueError")
