@@ -336,6 +336,9 @@ def main():
     fc.check_device_status(dev)
     value = world * passes * flops_step / (ms_step * 1e-3) / 1e12
     ms_step_no_gather = timed(step_no_gather, args.steps, 1) if world > 1 else None
+    if reassembly is not None:
+        reassembly.wait()    # no rank unmaps a buffer that a peer is still writing
+        reassembly.close()
 
     # ------------------------------------------------------------------ end to end (host buffers)
     # Every step copies its inputs from pinned host memory, runs forward + backward through the
@@ -504,8 +507,8 @@ def long_context_block(fc, parallel, dist, dev, world, rank, peaks, iters):
     """Long-context attention sharded by head: batch 2 x 32 heads x 65536 tokens x d 64, causal, bf16,
     dropout 0.  Rank r holds heads [r * 32 / N, (r + 1) * 32 / N); the data of a head does not
     depend on N (seeded per head).  Times this rank's forward + backward with and without the
-    all-gather of the output shards over NVLink (one collective per pass on a side stream, ordered
-    by streams); the slowest rank's time is reported.  FLOPs count half of the full problem
+    re-assembly of the output shards on every rank over NVLink (pitched peer copies on a side stream,
+    ordered by streams); the slowest rank's time is reported.  FLOPs count half of the full problem
     (4 d H B S^2 / 2)."""
     B, H, d, S = 2, HEADS_LONG, 64, 65536
     hs = H // world
@@ -522,15 +525,15 @@ def long_context_block(fc, parallel, dist, dev, world, rank, peaks, iters):
     cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=dev)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     side = torch.cuda.Stream(device=dev)
-    keep = {}
+    # (B * S, 32, d) on every rank, filled by pitched peer copies on the copy engines
+    full = parallel.PeerHeadGather(B * S, H, d, torch.bfloat16, dev) if world > 1 else None
 
     def one_pass(gather):
         out, lse = fc.fwd(q, k, v, cu, cu, S, S, 0.0, 0.125, False, True, False, None)
         if gather:
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                out.record_stream(side)
-                keep["full"] = parallel.all_gather_heads(out)      # (B * S, 32, d) on every rank
+                full.gather(out)
         fc.bwd(dout, q, k, v, out, lse, dq, dk, dv, cu, cu, S, S, 0.0, 0.125, False, True, None)
         if gather:
             torch.cuda.current_stream().wait_stream(side)
@@ -563,8 +566,10 @@ def long_context_block(fc, parallel, dist, dev, world, rank, peaks, iters):
         res["fwd_bwd_ms_with_gather"] = ms_gather
         res["fwd_bwd_tflops_per_gpu_with_gather"] = 3.5 * fl / ms_gather / 1e9
         res["gathered_bytes_per_gpu"] = int(B * S * H * d * 2)
-    del q, k, v, dout, dq, dk, dv
-    keep.clear()
+        res["gather"] = "peer copies (copy engines)" if full.uses_copy_engines else "NCCL all-gather"
+    if full is not None:
+        full.close()
+    del q, k, v, dout, dq, dk, dv, full
     return res
 
 

@@ -34,6 +34,10 @@ def _worker(rank, world, port, ok):
         pg.gather(tok)
         pg.wait()
         assert torch.equal(pg.buffer.view(-1, 8, 16), full[:10 * world])
+        hg = parallel.PeerHeadGather(37, 8, 16, full.dtype, full.device)
+        hg.gather(shard)
+        hg.wait()
+        assert torch.equal(hg.buffer, full)
         try:
             parallel.shard_heads(torch.zeros(3, 5, 4), world, rank)
             raise AssertionError("expected ValueError")

@@ -36,6 +36,17 @@ def _worker(rank, world, port, ok):
                 assert torch.all(pg.buffer[r] == float(10 * it + r + 1)), (it, r)
             dist.barrier()   # nobody overwrites a slot that a peer is still checking
         pg.close()
+        # head shards arrive in their final (total, heads, d) layout through pitched copies
+        g = torch.Generator().manual_seed(5)
+        full = torch.randn(777, 8, 64, generator=g).to(torch.bfloat16)
+        hg = parallel.PeerHeadGather(777, 8, 64, torch.bfloat16, dev)
+        assert hg.uses_copy_engines
+        with torch.cuda.stream(side):
+            hg.gather(parallel.shard_heads(full, world, rank).to(dev))
+            hg.wait()
+        assert torch.equal(hg.buffer.cpu(), full)
+        dist.barrier()
+        hg.close()
         ok[rank] = 1
     finally:
         dist.destroy_process_group()
