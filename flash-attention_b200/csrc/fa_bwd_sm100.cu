@@ -19,7 +19,8 @@
 //
 // Warp roles in bwd_main (512 threads):
 //   warps 0-3   compute group 0: key columns 0-63 of the tile, S, dP -> P~, dS (one thread per
-//               query row); dV epilogue
+//               query row; at d = 64 with dropout the 16x256b quad layout, in which one Philox call
+//               is private to a thread, and stmatrix stores); dV epilogue
 //   warps 4-7   compute group 1: key columns 64-127; dK epilogue
 //   warps 8-11  dQ group: tensor memory -> global reductions
 //   warp 12     TMA producer     warp 13  MMA issuer (S, dP, dQ; everything at d = 128)
@@ -509,6 +510,141 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int cbase = n0 + w * 64;  // first key column of this thread
     bool ok = true;
     FA_PROF_DECL
+    constexpr bool kQuad = DROPOUT && !Cfg::kTwoPhase;
+    if constexpr (kQuad) {
+      // ---- d = 64 with dropout: quad layout.  A warp reads its 32 query rows as two 16-row blocks
+      // (hh) with the 16x256b shape: a thread holds rows r8 and r8 + 8 of a block and two adjacent
+      // columns of every 8-column unit, which is the ownership pattern of the reference's mask
+      // generator (one Philox call = one thread's part of a 16 x 16 patch, QuadPhilox).  The packed
+      // pairs go to the swizzled P~ / dS tiles with stmatrix (8 x 8 matrices = 16-byte row chunks).
+      const int wq = warp & 3, lane = tid & 31;
+      const int r8 = lane >> 2, q4 = lane & 3;
+      constexpr uint32_t kHalf = 16u << 16;
+      QuadPhilox<4> qp;
+      qp.init(ka.drop, bh_sub, lane, w * 4);
+      // stmatrix row address of this lane: matrix k = lane / 8 is (row half k & 1, unit k >> 1)
+      const int st_row = wq * 32 + ((lane >> 3) & 1) * 8 + (lane & 7);   // + 16 * hh
+      const int st_unit = lane >> 4;                                     // + first unit of the quadruple
+      // per-row statistics (ri = hh * 2 + u) of the first tile; those of tile t + 1 are fetched while
+      // tile t is processed
+      float lse_nx[4], d_nx[4];
+      int32_t bs_nx[2] = {0, 0};
+      auto fetch_stats = [&](int t) {
+#pragma unroll
+        for (int ri = 0; ri < 4; ++ri) {
+          const int ig_n = q_tile(t) * kBM + wq * 32 + (ri >> 1) * 16 + (ri & 1) * 8 + r8;
+          const bool valid = ig_n < sq;
+          lse_nx[ri] = valid ? lse_row[ig_n] : INFINITY;
+          d_nx[ri] = valid ? d_row[ig_n] : 0.f;
+        }
+        if constexpr (BLOCKSPARSE) {
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int i16 = (q_tile(t) * kBM + wq * 32 + hh * 16) >> 4;
+            bs_nx[hh] = i16 < ka.bs_rows16
+                            ? ka.bs_iter[(static_cast<int64_t>(b) * ka.bs_kblocks + (n0 >> 8)) * ka.bs_rows16 + i16]
+                            : -1;
+          }
+        }
+      };
+      fetch_stats(0);
+      for (int t = 0; t < nm && ok; ++t) {
+        const int m0 = q_tile(t) * kBM;
+        const int row0 = m0 + wq * 32 + r8;  // + 16 * hh + 8 * u
+        float lse2[4], d_i[4];
+#pragma unroll
+        for (int ri = 0; ri < 4; ++ri) { lse2[ri] = lse_nx[ri] * 1.4426950408889634f; d_i[ri] = d_nx[ri]; }
+        const int32_t bs_it[2] = {bs_nx[0], bs_nx[1]};
+        if (t + 1 < nm) fetch_stats(t + 1);
+
+        // keep words of the thread's 2 x 4 patches (they do not depend on the scores: drawn before
+        // the wait).  kw[hh * 4 + grp][2 * u + half]: row u, columns 16 grp + 8 half + 2 q4 (+1 high)
+        uint32_t kw[8][4];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          int64_t it_tile;
+          if constexpr (BLOCKSPARSE) it_tile = bs_it[hh];
+          else it_tile = fa_iter_index(CAUSAL, n0 >> ka.drop.n_shift, (m0 + wq * 32 + hh * 16) >> 4, L16, ka.drop.n_shift);
+          qp.set_tile(ka.drop, it_tile, n0);
+#pragma unroll
+          for (int g4 = 0; g4 < 4; ++g4) qp.start(g4, kw[hh * 4 + g4]);
+        }
+#pragma unroll
+        for (int r = 2; r < 7; ++r)
+#pragma unroll
+          for (int k8 = 0; k8 < 8; ++k8) QuadPhilox<4>::round(ka.drop, kw[k8], r);
+
+        const bool need_mask = (n0 + kBN > sk) || (CAUSAL && (n0 + kBN - 1 > m0));
+        ok = mbar_wait(smem_u32(&sh.sdp_full), t & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        // everything goes to registers at once, so that the next tile's S and dP products can overwrite
+        // tensor memory while this tile is still being processed
+        uint32_t sr[2][32], dr[2][32];  // [hh][4 * unit + 2 * u + c]
+        tmem_ld_quad32(tS, sr[0]);
+        tmem_ld_quad32(tS + kHalf, sr[1]);
+        tmem_ld_quad32(tDP, dr[0]);
+        tmem_ld_quad32(tDP + kHalf, dr[1]);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&sh.sdp_consumed));
+
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t pp[16], pds[16];  // [2 * unit + u]: the stmatrix register order
+          const bool blk_in_layout = !BLOCKSPARSE || bs_it[hh] >= 0;
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int ri = hh * 2 + u;
+            const int ig = row0 + hh * 16 + u * 8;
+            const uint64_t nlse2 = pack_f2(-lse2[ri], -lse2[ri]);
+            const uint64_t nd2 = pack_f2(-d_i[ri], -d_i[ri]);
+#pragma unroll
+            for (int unit = 0; unit < 8; ++unit) {
+              const int i = 4 * unit + 2 * u;
+              float p0, p1;
+              unpack_f2(fma2(pack_f2(__uint_as_float(sr[hh][i]), __uint_as_float(sr[hh][i + 1])), c2, nlse2), p0, p1);
+              p0 = ex2f(p0);
+              p1 = ex2f(p1);
+              if (need_mask) {
+                const int col = cbase + unit * 8 + 2 * q4;
+                bool v0 = col < sk, v1 = col + 1 < sk;
+                if (CAUSAL) { v0 = v0 && (col <= ig); v1 = v1 && (col + 1 <= ig); }
+                if (!v0) p0 = 0.f;
+                if (!v1) p1 = 0.f;
+              }
+              if (BLOCKSPARSE && !blk_in_layout) { p0 = 0.f; p1 = 0.f; }
+              const uint32_t word = kw[hh * 4 + (unit >> 1)][2 * u + (unit & 1)];
+              const uint64_t p01 = pack_f2(p0, p1);
+              const uint64_t k01 = mul2(p01, pack_f2(fa_keep_factor_lo(word, thr_term), fa_keep_factor_hi(word, thr_term)));
+              float k0, k1, s0, s1;
+              unpack_f2(k01, k0, k1);
+              // dS = P~ * dP - P * D  (P~ = P where kept, 0 where dropped)
+              unpack_f2(fma2(k01, pack_f2(__uint_as_float(dr[hh][i]), __uint_as_float(dr[hh][i + 1])), mul2(p01, nd2)), s0, s1);
+              pp[2 * unit + u] = pack_lowp<BF16>(k0, k1);
+              pds[2 * unit + u] = pack_lowp<BF16>(s0, s1);
+            }
+          }
+          // the previous tile's products must have finished reading the P~ / dS buffers
+          if (hh == 0 && t > 0) {
+            ok = mbar_wait(smem_u32(&sh.pds_free), (t - 1) & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+          }
+          // four 8 x 8 matrices per instruction: (u = 0, 1) x (units a, a + 1) of the 64-column panel w
+          const int srow = st_row + hh * 16;
+#pragma unroll
+          for (int a2 = 0; a2 < 8; a2 += 2) {
+            const uint32_t off = w * 16384 + srow * 128 + (((a2 + st_unit) ^ (srow & 7)) << 4);
+            stmatrix_x4(smem_u32(p_ptr + off), pp[2 * a2], pp[2 * a2 + 1], pp[2 * a2 + 2], pp[2 * a2 + 3]);
+            stmatrix_x4(smem_u32(ds_ptr + off), pds[2 * a2], pds[2 * a2 + 1], pds[2 * a2 + 2], pds[2 * a2 + 3]);
+          }
+        }
+        if (!ok) break;
+        fence_async_smem();
+        mbar_arrive(smem_u32(&sh.pds_ready));
+      }
+    } else {
 
     // per-row statistics of the first tile; those of tile t + 1 are fetched while tile t is processed
     float lse_next = INFINITY, d_next = 0.f;
@@ -759,6 +895,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (w == 0 && row == 0) { FA_STAMP(t, 4) }
     }
     if (w == 0 && row == 0) { FA_PROF_FLUSH(8, nm) }
+    }  // row-per-thread layout
 
     // ---------------- epilogue: group 0 writes dV = acc / p_keep, group 1 writes dK = acc * scale / p_keep
     if (ok) {

@@ -209,18 +209,21 @@ struct LanePhilox {
 //   round 1   its word-2 input hi(M0 * c0) ^ c3 ^ key1 is the same for every call of a tile
 //             (the subsequence's high word is per (batch, head)), so M1 * that is per tile too.
 // A call therefore starts at round 1 with one multiply, then runs rounds 2..6: 11 multiplies.
+// NG: 16-column groups a thread covers per tile (8 = all 128 columns, 4 = one 64-column half).
+template <int NG>
 struct QuadPhilox {
-  uint32_t a_hi[8], b_lo[8];  // per 16-column group of a tile: hi(M1 * sub) ^ key0[0], lo(M1 * sub)
+  uint32_t a_hi[NG], b_lo[NG];  // per 16-column group: hi(M1 * sub) ^ key0[0], lo(M1 * sub)
   uint32_t sub_hi;
   // per (tile, 16-row block)
   uint32_t c1, n3k, w_hi, w_lo;
 
-  __device__ __forceinline__ void init(const DropoutParams& dp, int64_t bh_sub, int lane) {
+  // grp0: first 16-column group (of the 8 of a tile) this thread covers
+  __device__ __forceinline__ void init(const DropoutParams& dp, int64_t bh_sub, int lane, int grp0 = 0) {
     // bh_sub is a multiple of 256 and group * 32 + lane < 256: the sum never carries
-    const uint32_t sub_lo = static_cast<uint32_t>(bh_sub) + static_cast<uint32_t>(lane);
+    const uint32_t sub_lo = static_cast<uint32_t>(bh_sub) + static_cast<uint32_t>(grp0 * 32 + lane);
     sub_hi = static_cast<uint32_t>(static_cast<uint64_t>(bh_sub) >> 32);
 #pragma unroll
-    for (int grp = 0; grp < 8; ++grp) {
+    for (int grp = 0; grp < NG; ++grp) {
       const uint64_t v = mul_wide_u32(0xCD9E8D57u, sub_lo + grp * 32);
       a_hi[grp] = static_cast<uint32_t>(v >> 32) ^ dp.rk0[0];
       b_lo[grp] = static_cast<uint32_t>(v);
@@ -239,7 +242,7 @@ struct QuadPhilox {
     w_hi = static_cast<uint32_t>(w >> 32) ^ dp.rk0[1];
     w_lo = static_cast<uint32_t>(w);
   }
-  // State after rounds 0 and 1 of the call for 16-column group `grp` of the tile.
+  // State after rounds 0 and 1 of the call for the thread's 16-column group `grp` (0 .. NG-1).
   __device__ __forceinline__ void start(int grp, uint32_t (&s)[4]) const {
     const uint64_t p = mul_wide_u32(0xD2511F53u, a_hi[grp] ^ c1);
     s[0] = w_hi ^ b_lo[grp];

@@ -425,7 +425,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         (static_cast<int64_t>(b) * a.drop.heads_total + a.drop.head_offset + h) * 256;
     const int L16 = (sq + 15) >> 4;
     const int i16_base = (m0[g] + wq * 32) >> 4;  // 16-row block index of hh = 0
-    QuadPhilox qp;
+    QuadPhilox<8> qp;
     qp.init(a.drop, bh_sub, lane);
     const float thr_term = fa_keep_thr_term(a.drop.threshold);
 
@@ -464,7 +464,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
           for (int r = 2; r < 7; ++r)
 #pragma unroll
-            for (int k = 0; k < 8; ++k) QuadPhilox::round(a.drop, kw[k], r);
+            for (int k = 0; k < 8; ++k) QuadPhilox<8>::round(a.drop, kw[k], r);
         }
         if (hh == 0) {
           ok = mbar_wait(smem_u32(&sh.s_full[g]), j & 1, abort_flag);

@@ -315,4 +315,13 @@ __device__ __forceinline__ void tmem_st_pair32(uint32_t taddr, const uint32_t (&
 }
 
 
+// Four 8x8 matrices of 16-bit elements from registers to shared memory.  Register k of thread t holds
+// the elements (row t/4, columns 2(t%4) and 2(t%4)+1) of matrix k -- the pairs a thread owns in the quad
+// shapes above once packed to 16 bits; lane l supplies the address of row l%8 (16 bytes) of matrix l/8.
+__device__ __forceinline__ void stmatrix_x4(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(r0), "r"(r1),
+               "r"(r2), "r"(r3)
+               : "memory");
+}
+
 }  // namespace fa
