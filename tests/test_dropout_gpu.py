@@ -193,3 +193,67 @@ def test_philox_generator_against_curand(seed, offset):
     np.testing.assert_array_equal(orc.philox4x32(counter, key, rounds=10), cur)
     np.testing.assert_array_equal(orc.philox4x32(counter, key, rounds=7), run(7, 0))
     assert not np.array_equal(run(7, 0), cur)
+
+
+@pytest.mark.parametrize("d,dtype", [(64, torch.float16), (128, torch.bfloat16)])
+def test_mask_with_high_counter_and_subsequence_words(d, dtype):
+    """Philox state words that are zero in everyday calls: an offset beyond 2^34 (counter high word
+    1) and, through the head-shard option, a (batch, head) index beyond 2^24 (subsequence high word
+    1 and 2).  Forward mask through one-hot V, backward mask through one-hot dO, against the oracle."""
+    fc = _fc()
+    heads, p, causal = 2, 0.2, False
+    sq, sk = [150, 90], [150, 90]
+    seed, offset = 0x9E3779B97F4A7C15 & 0x7FFFFFFFFFFFFFFF, 2 ** 34 + 8
+    heads_total, head_offset = 2 ** 24 + 16, 2 ** 24 + 3
+    q, k, v, dout, cu_q, cu_k = U.make_varlen(sq, sk, heads, d, dtype, seed=17)
+    q, k = q * 0.1, k * 0.1
+    n = orc.mask_block_n(d, max(sk))
+    masks = [torch.from_numpy(np.stack([orc.dropout_keep_mask(seed, offset, b, head_offset + h, heads_total,
+                                                              sq[b], sk[b], p, n, causal) for h in range(heads)]))
+             for b in range(2)]
+    gen = torch.cuda.default_generators[torch.cuda.current_device()]
+
+    def rewind():
+        gen.manual_seed(seed)
+        gen.set_offset(offset)
+
+    with fc.head_shard(heads_total, head_offset):
+        for win in range(0, max(sk), d):
+            v.zero_()
+            start = 0
+            for nk in sk:
+                for c in range(d):
+                    if win + c < nk:
+                        v[start + win + c, :, c] = 1.0
+                start += nk
+            rewind()
+            out, lse = fc.fwd(q, k, v, cu_q, cu_k, max(sq), max(sk), p, d ** -0.5, False, causal, False, None)
+            qs = 0
+            for b, (nq, nk) in enumerate(zip(sq, sk)):
+                w = min(d, max(0, nk - win))
+                if w > 0:
+                    got = (out[qs:qs + nq, :, :w] != 0).permute(1, 0, 2).cpu()
+                    assert torch.equal(got, masks[b][:, :, win:win + w]), "forward, window %d of batch %d" % (win, b)
+                qs += nq
+        v.normal_()
+        rewind()
+        out, lse = fc.fwd(q, k, v, cu_q, cu_k, max(sq), max(sk), p, d ** -0.5, False, causal, False, None)
+        for win in range(0, max(sq), d):
+            dout.zero_()
+            start = 0
+            for nq in sq:
+                for c in range(d):
+                    if win + c < nq:
+                        dout[start + win + c, :, c] = 1.0
+                start += nq
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+            fc.bwd(dout, q, k, v, out, lse, dq, dk, dv, cu_q, cu_k, max(sq), max(sk), p, d ** -0.5, False,
+                   causal, None, philox=(seed, offset))
+            ks = 0
+            for b, (nq, nk) in enumerate(zip(sq, sk)):
+                w = min(d, max(0, nq - win))
+                if w > 0:
+                    got = (dv[ks:ks + nk, :, :w] != 0).permute(1, 2, 0).cpu()
+                    assert torch.equal(got, masks[b][:, win:win + w, :]), "backward, window %d of batch %d" % (win, b)
+                ks += nk
+    fc.check_device_status()
