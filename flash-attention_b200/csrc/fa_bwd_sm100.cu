@@ -69,6 +69,13 @@ struct BwdCfg {
   static constexpr int kSmemBytes = (2 + 2 * kQStages) * kTileBytes + 2 * kPdsBytes + kDqStageBytes + 1024;
   static constexpr uint32_t kTmemS = 0, kTmemDP = 128, kTmemDV = 256, kTmemDK = 256 + D;
   static constexpr uint32_t kTmemDQ = kAliasDq ? 128 : 256 + 2 * D;
+  // d = 64 leaves 64 tensor-memory columns free: a second copy of the 16-bit dS can go there and feed
+  // dQ = dS K as the A operand (its M dimension is the query row, like the lanes of S), so that
+  // product does not read dS from shared memory; dK = dS^T Q still takes the shared-memory copy.
+  // Used without dropout, where shared-memory bandwidth is the bound (8 x 12 x 4096: 1.49 -> 1.39 ms);
+  // with dropout the compute groups are the bound and the extra stores cost 2 %.
+  static constexpr bool kDsInTmemCapable = !kTwoPhase;
+  static constexpr uint32_t kTmemDS = 256 + 3 * D;
 };
 
 struct BwdShared {
@@ -130,6 +137,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
               const __grid_constant__ CUtensorMap tm_dq, const BwdArgs a) {
   using Cfg = BwdCfg<D, BLOCKSPARSE>;
+  constexpr bool kDsInTmem = Cfg::kDsInTmemCapable && !DROPOUT;
   extern __shared__ uint8_t smem_raw[];
   __shared__ BwdShared sh;
 
@@ -297,6 +305,13 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   };
   const uint32_t tS_ = tmem + Cfg::kTmemS, tDP_ = tmem + Cfg::kTmemDP;
   const uint32_t tDV_ = tmem + Cfg::kTmemDV, tDK_ = tmem + Cfg::kTmemDK, tDQ_ = tmem + Cfg::kTmemDQ;
+  const uint32_t tDS_ = tmem + Cfg::kTmemDS;
+  auto issue_dq_t = [&](uint32_t dst, uint32_t a_tmem, uint32_t b_base) {
+    // A = dS from tensor memory (16 keys = 8 columns per step); B = K [kv][d] read as N = d; K = kv
+#pragma unroll
+    for (int ks = 0; ks < kBN / 16; ++ks)
+      mma_ts(dst, a_tmem + ks * 8, make_smem_desc(b_base + ks * 2048, 16384, 1024), idesc_dq, ks > 0);
+  };
 
   if (warp >= 12) {
     // register split (per thread): d = 64: 192 compute / 72 dQ / 56 here; d = 128: 176 / 88 / 72
@@ -455,7 +470,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           }
           FA_PROF(4)
           // its tile is read out of tensor memory while dV / dK are still running
-          issue_dq(tDQ_, smem_ds, smem_k);
+          if constexpr (kDsInTmem) issue_dq_t(tDQ_, tDS_, smem_k);
+          else issue_dq(tDQ_, smem_ds, smem_k);
           mma_commit(smem_u32(&sh.dq_full));
           FA_STAMP(t, 10)
           mma_commit(smem_u32(&sh.pds_free));
@@ -885,10 +901,16 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           *reinterpret_cast<uint4*>(ds_ptr + off) =
               make_uint4(pds[4 * ch4], pds[4 * ch4 + 1], pds[4 * ch4 + 2], pds[4 * ch4 + 3]);
         }
+        // second copy of dS for the dQ product (32 keys = 16 packed columns of this half)
+        if constexpr (kDsInTmem) tmem_st16(tDS_ + lane_sel + w * 32 + c * 16, pds);
       }
       }
       if (!ok) break;
       FA_PROF(6)
+      if constexpr (kDsInTmem) {
+        tmem_wait_st();
+        tc_fence_before();
+      }
       fence_async_smem();
       mbar_arrive(smem_u32(&sh.pds_ready));
       FA_PROF(7)
