@@ -8,14 +8,17 @@
 //   warps 4-7   softmax group 1 (query tile 1)
 //   warp  8     TMA producer (Q once, K/V ring)
 //   warp  9     tcgen05.mma issuer (d = 128: every product; d = 64: S = Q K^T only)
-//   warp 10     d = 64: second issuer, O += P V (one thread sustains one instruction per ~93 clk)
+//   warp 10     d = 64: second issuer, O += P V (an issuing thread shares its scheduler with two
+//               softmax warps and gets an instruction out every 77-110 clk; two issuers keep S ahead)
 //   warp 11     idle
 // Tensor memory (512 columns): S0 [0,128) S1 [128,256) fp32 scores, O0 / O1 fp32 outputs behind
 // them.  The 16-bit probabilities P feed the P*V product straight from tensor memory; at d = 128
 // they overwrite the first 64 columns of their S buffer, at d = 64 they have columns of their own,
 // so the next score product can start as soon as the group has read its scores into registers.
-// The softmax groups are the bottleneck at d = 64 (exponentials on the special-function unit, the
-// dropout generator on the wide integer multiplies), the single issuing thread at d = 128.
+// The softmax groups are the bottleneck at every head size: their run time follows the sum of their
+// instruction costs (exponentials on the special-function unit, the dropout generator on the wide
+// integer multiplies, packed fp32 arithmetic), about 12 clk per score element and scheduler without
+// dropout and 25 with, against 4 (d = 64) or 8 (d = 128) clk of tensor-core time.
 //
 // Numerics follow the reference forward (csrc/flash_attn/src/fmha_fprop_kernel_1xN.h:365-638):
 // scores in fp32, p = exp2(scale*log2e*(s - max)), row sum of the un-dropped p, P rounded to the
