@@ -24,7 +24,7 @@
 //   warps 4-7   compute group 1: key columns 64-127; dK epilogue
 //   warps 8-11  dQ group: tensor memory -> global reductions
 //   warp 12     TMA producer     warp 13  MMA issuer (S, dP, dQ; everything at d = 128)
-//   warp 14     second MMA issuer (dV, dK) at d = 64      warp 15 idle
+//   warp 14, 15 second and third MMA issuer (dV | dK) at d = 64
 //
 // Schedules.  d = 64: Q and dO travel together through a three-stage ring; S and dP of tile t + 1
 // are issued as soon as the compute groups have read tile t into registers.  d = 128: shared
@@ -249,14 +249,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     mbar_init(smem_u32(&sh.kv_full), 1);
     for (int i = 0; i < 3; ++i) {
       mbar_init(smem_u32(&sh.q_full[i]), 1);
-      mbar_init(smem_u32(&sh.q_empty[i]), 1);
+      mbar_init(smem_u32(&sh.q_empty[i]), Cfg::kDualIssue ? 2 : 1);  // d = 64: dV (reads dO) and dK (reads Q)
     }
     mbar_init(smem_u32(&sh.do_full), 1);
     mbar_init(smem_u32(&sh.do_empty), 1);
     mbar_init(smem_u32(&sh.sdp_full), 1);
     mbar_init(smem_u32(&sh.sdp_consumed), 2 * kBM);
     mbar_init(smem_u32(&sh.pds_ready), 2 * kBM);
-    mbar_init(smem_u32(&sh.pds_free), Cfg::kDualIssue ? 2 : 1);
+    mbar_init(smem_u32(&sh.pds_free), Cfg::kDualIssue ? 3 : 1);  // d = 64: dQ, dV and dK each commit
     mbar_init(smem_u32(&sh.dq_full), 1);
     mbar_init(smem_u32(&sh.dq_consumed), kBM);
     mbar_init(smem_u32(&sh.dq_group), kBM);
@@ -480,7 +480,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         FA_PROF_FLUSH(16, nm)
       }
     } else if (warp == 14 && lane == 0 && Cfg::kDualIssue) {
-      // -------------------------------------------------------------- MMA issuer 2: dV, dK
+      // -------------------------------------------------------------- MMA issuer 2: dV
+      // dV and dK have a thread each: an issuing thread gets an instruction out every ~130 clk
+      // (it shares its scheduler with two compute warps), so the 16 instructions of the two products
+      // took longer to issue than to execute and the compute groups waited for the buffers.
       bool ok = true;
       FA_PROF_DECL
       for (int t = 0; t < nm && ok; ++t) {
@@ -493,13 +496,24 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_fence_after();
         issue_tt(tDV_, smem_p, smem_do + s * Cfg::kTileBytes, t > 0);
         FA_STAMP(t, 12)
-        issue_tt(tDK_, smem_ds, smem_q + s * Cfg::kTileBytes, t > 0);
-        FA_STAMP(t, 13)
         mma_commit(smem_u32(&sh.pds_free));
         mma_commit(smem_u32(&sh.q_empty[s]));
         FA_PROF(2)
       }
       FA_PROF_FLUSH(24, nm)
+    } else if (warp == 15 && lane == 0 && Cfg::kDualIssue) {
+      // -------------------------------------------------------------- MMA issuer 3: dK
+      bool ok = true;
+      for (int t = 0; t < nm && ok; ++t) {
+        const int s = t % Cfg::kQStages;
+        ok = mbar_wait(smem_u32(&sh.pds_ready), t & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        issue_tt(tDK_, smem_ds, smem_q + s * Cfg::kTileBytes, t > 0);
+        FA_STAMP(t, 13)
+        mma_commit(smem_u32(&sh.pds_free));
+        mma_commit(smem_u32(&sh.q_empty[s]));
+      }
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ compute groups
@@ -565,6 +579,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       };
       fetch_stats(0);
       for (int t = 0; t < nm && ok; ++t) {
+        FA_PROF(0)
         const int m0 = q_tile(t) * kBM;
         const int row0 = m0 + wq * 32 + r8;  // + 16 * hh + 8 * u
         float lse2[4], d_i[4];
@@ -591,9 +606,13 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           for (int k8 = 0; k8 < 8; ++k8) QuadPhilox<4>::round(ka.drop, kw[k8], r);
 
         const bool need_mask = (n0 + kBN > sk) || (CAUSAL && (n0 + kBN - 1 > m0));
+        FA_PROF(1)
+        if (w == 0 && row == 0) { FA_STAMP(t, 0) }
         ok = mbar_wait(smem_u32(&sh.sdp_full), t & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        FA_PROF(2)
+        if (w == 0 && row == 0) { FA_STAMP(t, 1) }
         tc_fence_after();
         // everything goes to registers at once, so that the next tile's S and dP products can overwrite
         // tensor memory while this tile is still being processed
@@ -605,6 +624,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(smem_u32(&sh.sdp_consumed));
+        if (w == 0 && row == 0) { FA_STAMP(t, 2) }
 
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
@@ -643,10 +663,13 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             }
           }
           // the previous tile's products must have finished reading the P~ / dS buffers
+          if (hh == 0) { FA_PROF(3) }
           if (hh == 0 && t > 0) {
             ok = mbar_wait(smem_u32(&sh.pds_free), (t - 1) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
           }
+          if (hh == 0) { FA_PROF(4) }
+          if (hh == 0 && w == 0 && row == 0) { FA_STAMP(t, 3) }
           // four 8 x 8 matrices per instruction: (u = 0, 1) x (units a, a + 1) of the 64-column panel w
           const int srow = st_row + hh * 16;
 #pragma unroll
@@ -657,9 +680,13 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           }
         }
         if (!ok) break;
+        FA_PROF(5)
         fence_async_smem();
         mbar_arrive(smem_u32(&sh.pds_ready));
+        FA_PROF(7)
+        if (w == 0 && row == 0) { FA_STAMP(t, 4) }
       }
+      if (w == 0 && row == 0) { FA_PROF_FLUSH(8, nm) }
     } else {
 
     // per-row statistics of the first tile; those of tile t + 1 are fetched while tile t is processed
