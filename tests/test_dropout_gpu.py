@@ -195,15 +195,17 @@ def test_philox_generator_against_curand(seed, offset):
     assert not np.array_equal(run(7, 0), cur)
 
 
-@pytest.mark.parametrize("d,dtype", [(64, torch.float16), (128, torch.bfloat16)])
-def test_mask_with_high_counter_and_subsequence_words(d, dtype):
+@pytest.mark.parametrize("d,dtype,offset", [(64, torch.float16, 2 ** 34 + 8), (128, torch.bfloat16, 2 ** 34 + 8),
+                                            (64, torch.float16, 2 ** 34 - 16), (128, torch.bfloat16, 2 ** 34 - 16)])
+def test_mask_with_high_counter_and_subsequence_words(d, dtype, offset):
     """Philox state words that are zero in everyday calls: an offset beyond 2^34 (counter high word
-    1) and, through the head-shard option, a (batch, head) index beyond 2^24 (subsequence high word
+    1), an offset just below it (the high word changes from 0 to 1 between the tiles of one launch)
+    and, through the head-shard option, a (batch, head) index beyond 2^24 (subsequence high word
     1 and 2).  Forward mask through one-hot V, backward mask through one-hot dO, against the oracle."""
     fc = _fc()
     heads, p, causal = 2, 0.2, False
     sq, sk = [150, 90], [150, 90]
-    seed, offset = 0x9E3779B97F4A7C15 & 0x7FFFFFFFFFFFFFFF, 2 ** 34 + 8
+    seed = 0x9E3779B97F4A7C15 & 0x7FFFFFFFFFFFFFFF
     heads_total, head_offset = 2 ** 24 + 16, 2 ** 24 + 3
     q, k, v, dout, cu_q, cu_k = U.make_varlen(sq, sk, heads, d, dtype, seed=17)
     q, k = q * 0.1, k * 0.1
