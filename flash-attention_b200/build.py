@@ -88,6 +88,55 @@ def build(force=False, verbose=False):
     return LIB_PATH
 
 
+BINDING_SRC = os.path.join(CSRC, "fa_torch_binding.cpp")
+BINDING_NAME = "_fa_binding"
+BINDING_PATH = os.path.join(OUT_DIR, BINDING_NAME + ".so")
+
+
+def build_binding(force=False):
+    """Compile the pybind11 / libtorch binding (csrc/fa_torch_binding.cpp) against libfa_b200.so with the
+    host compiler.  Returns the path of flash_attn_b200/_fa_binding.so.  The Python package works
+    without it (ctypes binding); with it a dense fwd / bwd call costs a few microseconds of host time."""
+    import sysconfig
+    import torch
+    from torch.utils import cpp_extension as ce
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    header = os.path.join(HERE, "..", "include", "fa_b200.h")
+    stamp = os.path.join(OBJ_DIR, "binding_stamp.txt")
+    h = hashlib.sha256()
+    for path in (BINDING_SRC, header):
+        with open(path, "rb") as f:
+            h.update(f.read())
+    h.update(torch.__version__.encode())
+    digest = h.hexdigest()
+    if (not force and os.path.exists(BINDING_PATH) and os.path.exists(stamp)
+            and open(stamp).read().strip() == digest):
+        return BINDING_PATH
+    try:
+        inc = ce.include_paths(device_type="cuda")
+        libs = ce.library_paths(device_type="cuda")
+    except TypeError:  # older signature
+        inc = ce.include_paths(cuda=True)
+        libs = ce.library_paths(cuda=True)
+    cmd = ([os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
+            "-DTORCH_EXTENSION_NAME=" + BINDING_NAME, "-DTORCH_API_INCLUDE_EXTENSION_H",
+            "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI)]
+           + ["-I" + i for i in inc] + ["-I" + sysconfig.get_paths()["include"], "-I" + os.path.dirname(header)]
+           + [BINDING_SRC, "-o", BINDING_PATH]
+           + ["-L" + l for l in libs] + ["-lc10", "-ltorch_cpu", "-ltorch", "-ltorch_python", "-lc10_cuda", "-ltorch_cuda"]
+           + ["-L" + OUT_DIR, "-lfa_b200", "-Wl,-rpath,$ORIGIN"] + ["-Wl,-rpath," + l for l in libs])
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    with open(os.path.join(OBJ_DIR, "fa_torch_binding.cpp.log"), "w") as f:
+        f.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
+    if r.returncode != 0:
+        raise RuntimeError("host compiler failed for %s:\n%s" % (BINDING_SRC, r.stderr[-4000:]))
+    with open(stamp, "w") as f:
+        f.write(digest)
+    return BINDING_PATH
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(path)
+    if "--no-binding" not in sys.argv:
+        print(build_binding(force="--force-binding" in sys.argv))
