@@ -1,9 +1,11 @@
-// Compiled binding of the dense attention entry points: the reference's extension module
-// (csrc/flash_attn/fmha_api.cpp: mha_fwd :173-299, mha_bwd :302-449) written against the C ABI of
-// libfa_b200.so.  Same argument checks, output allocation and Philox protocol as the Python (ctypes)
-// binding in flash_attn_b200/flash_attn_cuda.py, which stays the path for block-sparse calls,
-// return_softmax and for installations that did not build this file; what this one buys is host time:
-// a call costs a few microseconds instead of 20-30, which is the whole run time at short sequences.
+// Compiled binding of the attention entry points: the reference's extension module
+// (csrc/flash_attn/fmha_api.cpp: mha_fwd :173-299, mha_bwd :302-449, mha_fwd_block :451-573,
+// mha_bwd_block :575-718) written against the C ABI of libfa_b200.so.  Same argument checks, output
+// allocation and Philox protocol as the Python (ctypes) binding in flash_attn_b200/flash_attn_cuda.py,
+// which remains for installations that did not build this file; what this one buys is host time: a
+// call costs a few microseconds instead of 20-30, which is the whole run time at short sequences.
+// The block-sparse entry points are the dense ones with a converted block mask (the Python module
+// unpacks the reference's two call forms before it gets here).
 //
 // Things the reference's positional lists have no slot for arrive as trailing arguments from the
 // Python wrapper: the status buffer of the device, the head-shard pair of the dropout mask, the
@@ -112,30 +114,79 @@ void philox_state(const c10::optional<at::Generator>& gen_, uint64_t increment, 
 
 int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 
+// Block-sparse calls (fmha_api.cpp:451-573): checks of the converted mask and the scratch for the
+// per-sequence block-visit table.  The reference checks for exactly (ceil(max_k / 256), ceil16(max_q) /
+// 16) (:515); its own module passes a mask cut at a multiple of 256 rows' worth of slots, so a larger
+// mask is accepted and its real row length is used.
+void check_blockmask(const at::Tensor& blockmask, const at::Tensor& q, int64_t max_q, int64_t max_k) {
+  require(blockmask.is_cuda() && blockmask.scalar_type() == at::kInt && blockmask.is_contiguous(),
+          "blockmask must be a contiguous int32 CUDA tensor");
+  const int64_t want0 = round_up(max_k, 256) / 256, want1 = round_up(max_q, 16) / 16;
+  if (!(blockmask.dim() == 2 && blockmask.size(0) >= want0 && blockmask.size(1) >= want1)) {
+    std::string got = "(";
+    for (int64_t i = 0; i < blockmask.dim(); ++i) got += (i ? ", " : "") + std::to_string(blockmask.size(i));
+    if (blockmask.dim() == 1) got += ",";
+    throw std::runtime_error("blockmask must have at least shape (" + std::to_string(want0) + ", " +
+                             std::to_string(want1) + "), got " + got + ")");
+  }
+  require(q.scalar_type() == at::kHalf, "block-sparse attention is fp16 only");
+  require(q.size(2) == 16 || q.size(2) == 32 || q.size(2) == 64, "block-sparse attention supports head_dim 16, 32, 64");
+}
+
+at::Tensor attach_blockmask(fa_fwd_params& p, const at::Tensor& blockmask, const at::Tensor& q, int64_t batch) {
+  const size_t nbytes = fa_blocksparse_workspace_bytes(static_cast<int32_t>(batch), static_cast<int32_t>(blockmask.size(0)),
+                                                       static_cast<int32_t>(blockmask.size(1)));
+  at::Tensor ws = at::empty({static_cast<int64_t>(nbytes < 4 ? 4 : nbytes)}, q.options().dtype(at::kByte));
+  p.blockmask = static_cast<const int32_t*>(blockmask.data_ptr());
+  p.blockmask_rows = static_cast<int32_t>(blockmask.size(0));
+  p.blockmask_cols = static_cast<int32_t>(blockmask.size(1));
+  p.bs_workspace = ws.data_ptr();
+  p.bs_workspace_bytes = static_cast<size_t>(ws.numel());
+  return ws;
+}
+
 py::list fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& cu_q,
              const at::Tensor& cu_k, int64_t max_q, int64_t max_k, double p_dropout, double scale,
-             bool zero_tensors, bool causal, c10::optional<at::Generator> gen, bool return_philox,
-             int64_t mask_heads_total, int64_t mask_head_offset, int64_t status_ptr) {
+             bool zero_tensors, bool causal, bool return_softmax, c10::optional<at::Generator> gen,
+             c10::optional<at::Tensor> blockmask, bool return_philox, int64_t mask_heads_total,
+             int64_t mask_head_offset, int64_t status_ptr) {
   const Dims s = check_qkv(q, k, v, cu_q, cu_k);
   require(p_dropout < 1.0, "p_dropout must be < 1");
+  const bool sparse = blockmask.has_value();
+  if (sparse) check_blockmask(*blockmask, q, max_q, max_k);
   c10::cuda::CUDAGuard guard(q.device());
   const auto opts = q.options();
   const int64_t lse_len = round_up(max_q, 16);
-  at::Tensor o = zero_tensors ? at::zeros({s.total_q, s.heads, s.d}, opts) : at::empty({s.total_q, s.heads, s.d}, opts);
+  // the block-sparse entry always starts from o = 0 (:519)
+  at::Tensor o = (zero_tensors || sparse) ? at::zeros({s.total_q, s.heads, s.d}, opts)
+                                          : at::empty({s.total_q, s.heads, s.d}, opts);
   at::Tensor lse = zero_tensors
                        ? at::full({s.batch, s.heads, lse_len}, -std::numeric_limits<float>::infinity(), opts.dtype(at::kFloat))
                        : at::empty({s.batch, s.heads, lse_len}, opts.dtype(at::kFloat));
   uint64_t seed = 0, offset = 0;
   if (p_dropout > 0)
     philox_state(gen, fa_philox_increment(static_cast<int32_t>(s.d), static_cast<int32_t>(max_q),
-                                          static_cast<int32_t>(max_k), 0), seed, offset);
+                                          static_cast<int32_t>(max_k), sparse ? 1 : 0), seed, offset);
   fa_fwd_params p;
   fill_fwd(p, s, q, k, v, o, lse, cu_q, cu_k, max_q, max_k, p_dropout, scale, causal, seed, offset,
            mask_heads_total, mask_head_offset, status_ptr);
+  at::Tensor s_dmask, bs_ws;
+  if (return_softmax) {
+    // (batch, heads, seqlen_q rounded to 16, seqlen_k rounded as the reference does, :232-240, :253);
+    // zero outside the sequences
+    const int64_t base = sparse ? 256 : ((s.d == 128 && p_dropout > 0) ? 128 : 256);
+    const int64_t sk_r = (max_k <= 128 && !sparse) ? 128 : (max_k <= 256 ? 256 : round_up(max_k, base));
+    s_dmask = at::zeros({s.batch, s.heads, lse_len, sk_r}, opts);
+    p.s_dmask = s_dmask.data_ptr();
+    p.s_rows = lse_len;
+    p.s_cols = sk_r;
+  }
+  if (sparse) bs_ws = attach_blockmask(p, *blockmask, q, s.batch);
   check_rc(fa_fwd(&p, at::cuda::getCurrentCUDAStream().stream()));
   py::list res;
   res.append(o);
   res.append(lse);
+  if (return_softmax) res.append(s_dmask);
   if (return_philox) {
     res.append(py::int_(seed));
     res.append(py::int_(offset));
@@ -146,8 +197,9 @@ py::list fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, cons
 py::list bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
              const at::Tensor& out, const at::Tensor& lse, at::Tensor& dq, at::Tensor& dk, at::Tensor& dv,
              const at::Tensor& cu_q, const at::Tensor& cu_k, int64_t max_q, int64_t max_k, double p_dropout,
-             double scale, bool zero_tensors, bool causal, c10::optional<at::Generator> gen, int64_t stage_mask,
-             bool has_philox, uint64_t philox_seed, uint64_t philox_offset, bool deterministic,
+             double scale, bool zero_tensors, bool causal, c10::optional<at::Generator> gen,
+             c10::optional<at::Tensor> blockmask, int64_t stage_mask, bool has_philox, uint64_t philox_seed,
+             uint64_t philox_offset, bool deterministic,
              int64_t mask_heads_total, int64_t mask_head_offset, int64_t status_ptr) {
   const Dims s = check_qkv(q, k, v, cu_q, cu_k);
   const auto dt = q.scalar_type();
@@ -202,6 +254,11 @@ py::list bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, c
   p.workspace_bytes = static_cast<size_t>(ws.numel());
   p.stage_mask = static_cast<int32_t>(stage_mask);
   p.deterministic = deterministic ? 1 : 0;
+  at::Tensor bs_ws;
+  if (blockmask.has_value()) {
+    check_blockmask(*blockmask, q, max_q, max_k);
+    bs_ws = attach_blockmask(p.fwd, *blockmask, q, s.batch);
+  }
   check_rc(fa_bwd(&p, at::cuda::getCurrentCUDAStream().stream()));
   py::list res;
   res.append(dq);
@@ -214,7 +271,7 @@ py::list bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, c
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  m.doc() = "compiled binding of libfa_b200.so: dense fwd / bwd with the reference extension's argument lists";
+  m.doc() = "compiled binding of libfa_b200.so: fwd / bwd with the reference extension's argument lists (+ optional block mask)";
   m.def("fwd", &fwd);
   m.def("bwd", &bwd);
 }

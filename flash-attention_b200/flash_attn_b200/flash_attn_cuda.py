@@ -7,8 +7,8 @@ allocator), the current stream and the default CUDA generator's Philox state.
 
 Two routes into the library.  The ctypes route below is complete (every entry point and option).
 When the compiled binding `_fa_binding` (csrc/fa_torch_binding.cpp, built by build.py) is present,
-dense `fwd` / `bwd` calls without `return_softmax` go through it instead: same checks, allocation and
-Philox protocol in C++, a few microseconds of host time per call instead of 20-30.  Set
+the calls go through it instead: same checks, allocation and Philox protocol in C++, a few
+microseconds of host time per call instead of 20-30.  Set
 FA_B200_BINDING=ctypes to keep everything on the ctypes route.
 """
 import ctypes
@@ -29,7 +29,7 @@ if os.environ.get("FA_B200_BINDING", "") != "ctypes":
 
 
 def binding_in_use():
-    """'compiled' when dense calls go through the C++ binding, else 'ctypes'."""
+    """'compiled' when calls go through the C++ binding, else 'ctypes'."""
     return "compiled" if _binding is not None else "ctypes"
 
 
@@ -258,15 +258,15 @@ def _check_blockmask(blockmask, max_seqlen_q, max_seqlen_k, q):
 def _run_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout,
              softmax_scale, zero_tensors, is_causal, return_softmax, gen, blockmask=None,
              return_philox=False):
-    if _binding is not None and blockmask is None and not return_softmax:
+    if _binding is not None:
         dev = q.device
         sp = _status_ptr.get(dev)
         if sp is None:
             sp = _status_buffer(dev).data_ptr()
         mh = options.mask_heads or (0, 0)
         return _binding.fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, int(max_seqlen_q), int(max_seqlen_k),
-                            float(p_dropout), float(softmax_scale), bool(zero_tensors), bool(is_causal), gen,
-                            return_philox, mh[0], mh[1], sp)
+                            float(p_dropout), float(softmax_scale), bool(zero_tensors), bool(is_causal),
+                            bool(return_softmax), gen, blockmask, return_philox, mh[0], mh[1], sp)
     batch, total_q, total_k, heads, d = _check_qkv(q, k, v, cu_seqlens_q, cu_seqlens_k)
     _require(p_dropout < 1.0, "p_dropout must be < 1")
     sparse = blockmask is not None
@@ -357,7 +357,7 @@ def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
     philox (keyword, not in the reference): the (seed, offset) pair `fwd(..., return_philox=True)`
     handed back; the mask is then regenerated from it and the generator is left alone (the
     reference's callers restore the generator state around this call instead)."""
-    if _binding is not None and _blockmask is None:
+    if _binding is not None:
         dev = q.device
         sp = _status_ptr.get(dev)
         if sp is None:
@@ -366,7 +366,7 @@ def bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
         has_philox = philox is not None
         return _binding.bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
                             int(max_seqlen_q), int(max_seqlen_k), float(p_dropout), float(softmax_scale),
-                            bool(zero_tensors), bool(is_causal), gen, int(_stage_mask), has_philox,
+                            bool(zero_tensors), bool(is_causal), gen, _blockmask, int(_stage_mask), has_philox,
                             int(philox[0]) if has_philox else 0, int(philox[1]) if has_philox else 0,
                             bool(options.deterministic), mh[0], mh[1], sp)
     batch, total_q, total_k, heads, d = _check_qkv(q, k, v, cu_seqlens_q, cu_seqlens_k)

@@ -121,3 +121,39 @@ def test_zero_tensors_head_shard_and_errors():
         with _ctypes_route(), pytest.raises(RuntimeError) as e2:
             bad()
         assert str(e1.value).splitlines()[0] == str(e2.value).splitlines()[0]
+
+
+def test_block_sparse_and_return_softmax_through_both_routes():
+    _require_compiled()
+    fc = _fc()
+    from flash_attn_b200.flash_blocksparse_attn_interface import convert_blockmask
+    S = 512
+    torch.manual_seed(2)
+    blocks = (torch.rand(S // 256, S // 256) < 0.5) | torch.eye(S // 256, dtype=torch.bool)
+    conv = convert_blockmask(blocks.repeat_interleave(16, dim=0).to(torch.int32).cuda(), False)
+    q, k, v, dout, cu_q, cu_k = U.make_varlen([S, 300], [S, 300], 2, 64, torch.float16, seed=34)
+
+    def run():
+        torch.cuda.manual_seed(8)
+        out, lse, seed, offset = fc.fwd_block(q, k, v, cu_q, cu_k, conv, S, S, 0.1, 0.125, False, False, None,
+                                              return_philox=True)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        fc.bwd_block(dout, q, k, v, out, lse, dq, dk, dv, cu_q, cu_k, conv, S, S, 0.1, 0.125, False, None,
+                     philox=(seed, offset))
+        torch.cuda.manual_seed(8)
+        o2, _, s_dmask = fc.fwd(q, k, v, cu_q, cu_k, S, S, 0.1, 0.125, False, True, True, None)
+        return out, dk, dv, o2, s_dmask
+
+    a = run()
+    with _ctypes_route():
+        b = run()
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+    # the messages of the block-mask checks agree too
+    for bad in (lambda: fc.fwd_block(q, k, v, cu_q, cu_k, conv[:1], S, S, 0.0, 0.125, False, False, None),
+                lambda: fc.fwd_block(q, k, v, cu_q, cu_k, conv.long(), S, S, 0.0, 0.125, False, False, None)):
+        with pytest.raises(RuntimeError) as e1:
+            bad()
+        with _ctypes_route(), pytest.raises(RuntimeError) as e2:
+            bad()
+        assert str(e1.value).splitlines()[0] == str(e2.value).splitlines()[0]
