@@ -259,3 +259,32 @@ def test_mask_with_high_counter_and_subsequence_words(d, dtype, offset):
                     assert torch.equal(got, masks[b][:, win:win + w, :]), "backward, window %d of batch %d" % (win, b)
                 ks += nk
     fc.check_device_status()
+
+
+@pytest.mark.parametrize("dtype,p", [(torch.float16, 0.05), (torch.bfloat16, 0.25)])
+def test_rows_with_a_single_key_leave_only_the_rounding_of_o_in_dq(dtype, p):
+    """Where a query sees one key its softmax is 1, dS is 0 and so is dq in exact arithmetic (and in
+    the oracle, whose softmax backward computes g - sum(g * a) = 0).  A FlashAttention backward takes
+    D = rowsum(dO * O) from the 16-bit O (csrc/flash_attn/src/fmha_dgrad_kernel_1xN_loop.h:16-28,
+    :225), so dP - D keeps the rounding of O: |dq| <= eps * sum_c |dO_c O_c| * |k| * scale with eps one
+    unit in the last place of the 16-bit type.  The '2 x the 16-bit program's error' rule cannot hold
+    against an error of exactly zero; this is the bound that does."""
+    fc = _fc()
+    d, heads, nq = 64, 2, 63
+    q, k, v, dout, cu_q, cu_k = U.make_varlen([nq], [1], heads, d, dtype, seed=23)
+    scale = d ** -0.5
+    torch.cuda.manual_seed(4)
+    out, lse, seed, offset = fc.fwd(q, k, v, cu_q, cu_k, nq, 1, p, scale, False, False, False, None,
+                                    return_philox=True)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    fc.bwd(dout, q, k, v, out, lse, dq, dk, dv, cu_q, cu_k, nq, 1, p, scale, False, False, None,
+           philox=(seed, offset))
+    fc.check_device_status()
+    eps = 2.0 ** (-10 if dtype is torch.float16 else -7)
+    bound = eps * (dout.float() * out.float()).abs().sum(-1).max() * k.float().abs().max() * scale
+    err = dq.float().abs().max()
+    assert 0 < err <= bound, (float(err), float(bound))
+    # kept rows hold v / p_keep, dropped rows zero: the forward is exact up to that rounding
+    kept = (out.float().abs().sum(-1) > 0)
+    want = (v.float() / (1 - p)).expand_as(out.float())
+    assert U.max_err(out[kept], want[kept]) <= eps * want.abs().max()
